@@ -1,0 +1,152 @@
+// Embedding gather, fused residual-add + RMSNorm, SiLU-mul, residual add.
+//
+// The residual stream is float in both engine precisions: the sum over layers
+// is formed in 32-bit, and only what feeds a matrix product is rounded to the
+// activation type.  The reference rounds the stream to bf16 after every add
+// (cuda/kernels/bf16_kernels.cu:504-517) and runs norm and add as separate
+// kernels (src/engine/batched_engine.ts:1164-1178).
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// out[t, :] = table[ids[t], :] * scale   (cuda/kernels/bf16_kernels.cu:711-729,
+// which does not check the id; here a bad id sets an error bit and yields zeros).
+template <typename W>
+__global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int H, int vocab, float scale,
+                                    int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * H;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, BF_ERR_TOKEN_ID);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const W* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = bf_ld(row + i) * scale;
+}
+
+BF_EXPORT int bf_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
+                              int T, int H, int vocab, float scale, int* err,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == BF_DTYPE_F32)
+    embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H,
+                                                          vocab, scale, err);
+  else
+    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+        (const __nv_bfloat16*)table, ids, out, H, vocab, scale, err);
+  return bf_launch_status();
+}
+
+// -------------------------------------------------------- add + RMSNorm (fused)
+// For output row i (source row r = rows ? rows[i] : i):
+//   x = resid[r] + (delta ? delta[r] : 0);  if (write_back) resid[r] = x;
+//   out[i] = x * rsqrt(mean(x^2) + eps) * w           (bf16_kernels.cu:40-84)
+// One block per row; the row is kept in shared memory between the two passes.
+template <typename A>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
+                                   const float* __restrict__ w, A* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps,
+                                   int write_back) {
+  extern __shared__ float sh[];
+  float* row = sh;            // H floats
+  float* scratch = sh + H;    // 33 floats
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* x = resid + (size_t)r * H;
+  const A* d = delta ? delta + (size_t)r * H : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = x[c];
+    if (d) v += bf_ld(d + c);
+    row[c] = v;
+    if (write_back && d) x[c] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  A* o = out + (size_t)i * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) bf_st(o + c, row[c] * inv * w[c]);
+}
+
+BF_EXPORT int bf_add_rmsnorm(float* resid, const void* delta, const float* w, void* out,
+                             const int* rows, int n_rows, int H, float eps, int act_dtype,
+                             int write_back, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (act_dtype == BF_DTYPE_F32) {
+    auto k = add_rmsnorm_kernel<float>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<n_rows, threads, smem, stream>>>(resid, (const float*)delta, w, (float*)out, rows, H,
+                                         eps, write_back);
+  } else {
+    auto k = add_rmsnorm_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<n_rows, threads, smem, stream>>>(resid, (const __nv_bfloat16*)delta, w,
+                                         (__nv_bfloat16*)out, rows, H, eps, write_back);
+  }
+  return bf_launch_status();
+}
+
+// --------------------------------------------------------------- residual add
+// resid[t, :] += delta[t, :]   (used when an add cannot ride on a following norm)
+template <typename A>
+__global__ void residual_add_kernel(float* __restrict__ resid, const A* __restrict__ delta,
+                                    size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) resid[i] += bf_ld(delta + i);
+}
+
+BF_EXPORT int bf_residual_add(float* resid, const void* delta, long long n, int act_dtype,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (act_dtype == BF_DTYPE_F32)
+    residual_add_kernel<float><<<(int)blocks, threads, 0, stream>>>(resid, (const float*)delta,
+                                                                    (size_t)n);
+  else
+    residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+        resid, (const __nv_bfloat16*)delta, (size_t)n);
+  return bf_launch_status();
+}
+
+// ------------------------------------------------------------------- SiLU-mul
+// out[t, c] = silu(gu[t, c]) * gu[t, I + c],  silu(g) = g / (1 + exp(-g))
+// (cuda/kernels/bf16_kernels.cu:461-477; there gate and up are separate buffers,
+// here they are the two halves of one fused projection's output row).
+template <typename A>
+__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, int T, int I) {
+  const size_t n = (size_t)T * I;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    const size_t t = i / I, c = i - t * I;
+    const float g = bf_ld(gu + t * 2 * I + c);
+    const float u = bf_ld(gu + t * 2 * I + I + c);
+    bf_st(out + i, g / (1.f + expf(-g)) * u);
+  }
+}
+
+BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype,
+                          cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int threads = 256;
+  long long blocks = ((long long)T * I + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (act_dtype == BF_DTYPE_F32)
+    silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out,
+                                                               T, I);
+  else
+    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
+  return bf_launch_status();
+}

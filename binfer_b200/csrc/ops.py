@@ -1,0 +1,197 @@
+"""Python bindings of the CUDA library: one function per kernel launcher.
+
+Tensors are passed as raw device pointers through ctypes, on torch's current
+stream.  There is no fallback of any kind: if the library cannot be built or
+loaded, or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_lib = None
+_launches = 0      # kernels of this library launched so far (for the bench's count)
+
+_c_int, _c_ll, _c_float, _c_void_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; built on first use."""
+    global _lib
+    if _lib is None:
+        path = build.ensure_built()
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the engine's CUDA library {path}: {e}") from None
+    return _lib
+
+
+def launches() -> int:
+    return _launches
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"unsupported activation dtype {t.dtype} (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
+    if t is None:
+        return _c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("the engine's kernels take CUDA tensors only (no CPU path)")
+    return _c_void_p(t.data_ptr())
+
+
+def _stream() -> _c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _want(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float,
+                 err: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] * scale; out is the float residual stream [T, H]."""
+    _want(ids, torch.int32, "ids"); _want(out, torch.float32, "out")
+    T, H = out.shape
+    code = lib().bf_embed_gather(_ptr(table), _c_int(_dtype_code(table)), _ptr(ids), _ptr(out),
+                                 _c_int(T), _c_int(H), _c_int(table.shape[0]), _c_float(scale),
+                                 _ptr(err), _stream())
+    _check(code, "embed_gather")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                write_back: bool = True) -> None:
+    """out[i] = rmsnorm(resid[r] + delta[r]) * weight with r = rows[i] (or i); the
+    sum is written back to resid when ``write_back``."""
+    _want(resid, torch.float32, "resid"); _want(weight, torch.float32, "weight")
+    n, H = out.shape
+    if delta is not None and (delta.dtype != out.dtype or not delta.is_contiguous()):
+        raise KernelError("delta must be contiguous and of the output's dtype")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    code = lib().bf_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
+                                _c_int(n), _c_int(H), _c_float(eps), _c_int(_dtype_code(out)),
+                                _c_int(1 if write_back else 0), _stream())
+    _check(code, "add_rmsnorm")
+
+
+def residual_add(resid: torch.Tensor, delta: torch.Tensor) -> None:
+    _want(resid, torch.float32, "resid")
+    code = lib().bf_residual_add(_ptr(resid), _ptr(delta), _c_ll(resid.numel()),
+                                 _c_int(_dtype_code(delta)), _stream())
+    _check(code, "residual_add")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]."""
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or gate_up.dtype != out.dtype:
+        raise KernelError("silu_mul: gate_up must be contiguous [T, 2*I] of the output's dtype")
+    code = lib().bf_silu_mul(_ptr(gate_up), _ptr(out), _c_int(T), _c_int(I),
+                             _c_int(_dtype_code(out)), _stream())
+    _check(code, "silu_mul")
+
+
+# ------------------------------------------------------------------- attention
+def qk_norm_rope_kv_write(qkv: torch.Tensor, q_w: Optional[torch.Tensor],
+                          k_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                          positions: torch.Tensor, slots: Optional[torch.Tensor],
+                          q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor], nh: int, nkv: int, d: int,
+                          eps: float, err: torch.Tensor) -> None:
+    """Per-head RMSNorm of q and k, rotation, q to ``q_out [T, nh*d]``, k and v into
+    cache pages ``[pages, nkv, page_size, d]`` at ``slots``."""
+    T = qkv.shape[0]
+    if qkv.stride(1) != 1:
+        raise KernelError("qkv rows must be contiguous")
+    rot_half = 0 if inv_freq is None else inv_freq.numel()
+    page_size = k_cache.shape[2] if k_cache is not None else 1
+    num_slots = k_cache.shape[0] * page_size if k_cache is not None else 0
+    if k_cache is not None and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError("cache pages must be contiguous")
+    code = lib().bf_qk_norm_rope_kv_write(
+        _ptr(qkv), _c_ll(qkv.stride(0)), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _c_int(rot_half),
+        _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(T),
+        _c_int(nh), _c_int(nkv if k_cache is not None else 0), _c_int(d), _c_int(page_size),
+        _c_ll(num_slots), _c_float(eps), _c_int(_dtype_code(qkv)), _ptr(err), _stream())
+    _check(code, "qk_norm_rope_kv_write")
+
+
+def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                            seq_of_token: torch.Tensor, positions: torch.Tensor,
+                            block_tables: torch.Tensor, out: torch.Tensor, nh: int, nkv: int,
+                            d: int, window: Optional[int], scale: float,
+                            err: torch.Tensor) -> None:
+    T = q.shape[0]
+    if d > 256:
+        raise KernelError(f"attention: head_dim {d} is not supported (at most 256)")
+    code = lib().bf_paged_attention_generic(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_of_token), _ptr(positions),
+        _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(T), _c_int(nh),
+        _c_int(nkv), _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
+        _c_int(window or 0), _c_float(scale), _c_int(_dtype_code(q)), _ptr(err), _stream())
+    _check(code, "paged_attention_generic")
+
+
+# ------------------------------------------------------------- matrix products
+def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic."""
+    for t, n in ((a, "a"), (w, "w"), (out, "out")):
+        if t.dtype != torch.float32 or t.stride(-1) != 1:
+            raise KernelError(f"sgemm_nt: {n} must be float32 with contiguous rows")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"sgemm_nt: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> "
+                          f"{tuple(out.shape)} do not agree")
+    code = lib().bf_sgemm_nt(_ptr(a), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K),
+                             _c_ll(a.stride(0)), _c_ll(w.stride(0)), _c_ll(out.stride(0)),
+                             _stream())
+    _check(code, "sgemm_nt")
+
+
+# -------------------------------------------------------------------- sampling
+def repetition_penalty(logits: torch.Tensor, items: torch.Tensor, penalty: torch.Tensor) -> None:
+    """items: int32 [n, 3] of (row, token, count)."""
+    _want(logits, torch.float32, "logits"); _want(items, torch.int32, "items")
+    code = lib().bf_repetition_penalty(_ptr(logits), _c_int(logits.shape[1]), _ptr(items),
+                                       _c_int(items.shape[0]), _ptr(penalty), _stream())
+    _check(code, "repetition_penalty")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+    _want(logits, torch.float32, "logits"); _want(temperature, torch.float32, "temperature")
+    _want(top_k, torch.int32, "top_k"); _want(top_p, torch.float32, "top_p")
+    _want(uniform, torch.float32, "uniform"); _want(out, torch.int32, "out")
+    R, V = logits.shape
+    code = lib().bf_sample(_ptr(logits), _c_int(R), _c_int(V), _ptr(temperature), _ptr(top_k),
+                           _ptr(top_p), _ptr(uniform), _ptr(out), _stream())
+    _check(code, "sample")

@@ -1,0 +1,125 @@
+"""Replay on the GPU against the plain implementation: whole, decoded tail, portions, mixed.
+
+Every regime must give, at every position, the logits that the plain whole-sequence
+implementation gives; float32 within float32 rounding, bfloat16 within bfloat16
+rounding of the activations (the plain side reads the same bfloat16 weights).
+"""
+import pytest
+import torch
+
+import helpers as H
+import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+# largest |difference| / largest |reference logit|
+TOL = {torch.float32: 2e-5, torch.bfloat16: 3e-2}
+# and root-mean-square of the difference over that of the reference
+TOL_RMS = {torch.float32: 5e-6, torch.bfloat16: 1e-2}
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 70], "W": [3, 30, 64, 101]}
+
+
+def _requests(which, extra=()):
+    vocab = H.TINY[which]["raw"]["vocab_size"]
+    lens = list(LENGTHS[which]) + list(extra)
+    return {f"r{i}": H.random_tokens(n, vocab, 100 * i + n) for i, n in enumerate(lens)}
+
+
+@pytest.fixture(scope="module")
+def plain_logits(tmp_path_factory):
+    """Reference logits per (config, dtype, request), computed once in float64."""
+    cache = {}
+
+    def get(which, dtype, reqs):
+        key = (which, dtype)
+        d = H.make_model_dir(tmp_path_factory.getbasetemp(), which, dtype)
+        raw, w = H.read_model_dir(d)
+        out = cache.setdefault(key, {})
+        for rid, toks in reqs.items():
+            k = (rid, tuple(toks))
+            if k not in out:
+                out[k] = P.forward(raw, w, toks, dtype=torch.float64)
+        return d, {rid: out[(rid, tuple(toks))] for rid, toks in reqs.items()}
+
+    return get
+
+
+def _runner(model_dir, dtype, page_size, num_pages):
+    from binfer_b200.engine import make_env, make_runner, model_from_dir
+    env = make_env(dtype)
+    model = model_from_dir(model_dir, env)
+    return make_runner(model, env, page_size=page_size, num_pages=num_pages, max_requests=8)
+
+
+def _compare(got, ref, dtype, what):
+    assert got, "the trace produced no logits"
+    worst, worst_at = 0.0, None
+    for (rid, pos), row in got.items():
+        e = H.rel_err(row, ref[rid][pos])
+        if e > worst:
+            worst, worst_at = e, (rid, pos)
+    assert worst <= TOL[dtype], f"{what}: worst relative error {worst:.3g} at {worst_at}"
+    g = torch.stack([row for row in got.values()])
+    r = torch.stack([ref[rid][pos] for (rid, pos) in got])
+    assert H.rel_rms(g, r) <= TOL_RMS[dtype], f"{what}: rms error {H.rel_rms(g, r):.3g}"
+    # every position of every request was produced
+    for rid, lg in ref.items():
+        assert all((rid, p) in got for p in range(lg.shape[0])), f"{what}: {rid} incomplete"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which", ["A", "B", "W"])
+@pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
+def test_replay(cuda_device, plain_logits, which, dtype, regime):
+    extra = (55, 61) if regime == "mixed" else ()
+    reqs = _requests(which, extra)
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    steps = {"whole": H.trace_whole, "tail": H.trace_decode_tail,
+             "portions": H.trace_portions, "mixed": H.trace_mixed}[regime](reqs)
+    ps = H.TINY[which]["page_size"]
+    # exactly the peak need: every page that is given back is handed out again
+    runner = _runner(model_dir, dtype, ps, H.peak_pages(steps, ps))
+    got = H.run_trace(runner, steps)
+    assert not runner.cache.requests, "a finished request still holds pages"
+    assert all(g.pool.num_held == 0 for g in runner.cache.groups)
+    _compare(got, ref, dtype, f"{which}/{regime}")
+
+
+@pytest.mark.parametrize("which", ["A", "B", "W"])
+def test_regimes_agree_bitwise_in_float32(cuda_device, plain_logits, which):
+    """In float32 the order of every sum is fixed by the position alone, so cutting
+    and batching change nothing at all."""
+    reqs = _requests(which)
+    model_dir, _ = plain_logits(which, torch.float32, reqs)
+    ps = H.TINY[which]["page_size"]
+    outs = []
+    for make in (H.trace_whole, H.trace_decode_tail, H.trace_portions, H.trace_mixed):
+        steps = make(reqs)
+        outs.append(H.run_trace(_runner(model_dir, torch.float32, ps, H.peak_pages(steps, ps)),
+                                steps))
+    for other in outs[1:]:
+        for key, row in outs[0].items():
+            assert torch.equal(row, other[key]), f"{which}: logits at {key} depend on the cut"
+
+
+def test_long_decoding(cuda_device, plain_logits):
+    """A short prompt, then 300 tokens one by one (across many pages)."""
+    which, dtype = "B", torch.float32
+    vocab = H.TINY[which]["raw"]["vocab_size"]
+    reqs = {"long": H.random_tokens(304, vocab, 7)}
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    steps = H.trace_decode_tail(reqs, tail=300)
+    runner = _runner(model_dir, dtype, 8, H.peak_pages(steps, 8))
+    _compare(H.run_trace(runner, steps), ref, dtype, "long decoding")
+
+
+def test_first_tokens(cuda_device, plain_logits):
+    """The first tokens of a sequence, one per step from the very start."""
+    for which in ("A", "B"):
+        vocab = H.TINY[which]["raw"]["vocab_size"]
+        reqs = {"s": H.random_tokens(6, vocab, 3)}
+        model_dir, ref = plain_logits(which, torch.float32, reqs)
+        steps = H.trace_decode_tail(reqs, tail=5)
+        runner = _runner(model_dir, torch.float32, H.TINY[which]["page_size"], 4)
+        _compare(H.run_trace(runner, steps), ref, torch.float32, f"{which}/first tokens")
