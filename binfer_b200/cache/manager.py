@@ -135,14 +135,20 @@ class CacheManager:
             out.append(add - release)
         return out
 
-    def can_reserve(self, wants: Sequence[Tuple[Hashable, int]]) -> bool:
-        """Whether ``reserve`` would succeed for all ``(rid, new_len)`` together."""
+    def free_after(self, wants: Sequence[Tuple[Hashable, int]]) -> List[int]:
+        """Free pages each group would have left after reserving every ``(rid, new_len)``
+        (negative: that many pages short)."""
         need = [0] * len(self.groups)
         for rid, new_len in wants:
             rc = self.requests[rid]
             for i, n in enumerate(self.pages_to_add(rc, new_len)):
                 need[i] += n
-        return all(n <= g.pool.num_free for n, g in zip(need, self.groups))
+        return [g.pool.num_free - n for n, g in zip(need, self.groups)]
+
+    def can_reserve(self, wants: Sequence[Tuple[Hashable, int]], spare: int = 0) -> bool:
+        """Whether ``reserve`` would succeed for all ``(rid, new_len)`` together and still
+        leave ``spare`` pages free in every group."""
+        return all(n >= spare for n in self.free_after(wants))
 
     def reserve(self, rid: Hashable, new_len: int) -> None:
         """Make the block tables of ``rid`` cover positions < ``new_len``.

@@ -66,6 +66,37 @@ def _check(code: int, what: str) -> None:
         raise KernelError(f"{what}: CUDA error {code}")
 
 
+_profiler = None   # an object with begin(name) / end(name), set by binfer_b200.profiling
+
+
+def set_profiler(p) -> None:
+    global _profiler
+    _profiler = p
+
+
+def _run(name: str, fn, *args) -> None:
+    p = _profiler
+    if p is not None:
+        p.begin(name)
+    code = fn(*args)
+    if p is not None:
+        p.end(name)
+    _check(code, name)
+
+
+def count_library_launch(name: str = "gemm") -> None:
+    """A library matrix product was launched (counted apart from the engine's own kernels)."""
+    global _library_launches
+    _library_launches += 1
+
+
+_library_launches = 0
+
+
+def library_launches() -> int:
+    return _library_launches
+
+
 def _want(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
     if t.dtype != dtype:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
@@ -79,10 +110,9 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scal
     """out[t] = table[ids[t]] * scale; out is the float residual stream [T, H]."""
     _want(ids, torch.int32, "ids"); _want(out, torch.float32, "out")
     T, H = out.shape
-    code = lib().bf_embed_gather(_ptr(table), _c_int(_dtype_code(table)), _ptr(ids), _ptr(out),
+    _run("embed_gather", lib().bf_embed_gather, _ptr(table), _c_int(_dtype_code(table)), _ptr(ids), _ptr(out),
                                  _c_int(T), _c_int(H), _c_int(table.shape[0]), _c_float(scale),
                                  _ptr(err), _stream())
-    _check(code, "embed_gather")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -96,17 +126,15 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         raise KernelError("delta must be contiguous and of the output's dtype")
     if rows is not None:
         _want(rows, torch.int32, "rows")
-    code = lib().bf_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
+    _run("add_rmsnorm", lib().bf_add_rmsnorm, _ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
                                 _c_int(n), _c_int(H), _c_float(eps), _c_int(_dtype_code(out)),
                                 _c_int(1 if write_back else 0), _stream())
-    _check(code, "add_rmsnorm")
 
 
 def residual_add(resid: torch.Tensor, delta: torch.Tensor) -> None:
     _want(resid, torch.float32, "resid")
-    code = lib().bf_residual_add(_ptr(resid), _ptr(delta), _c_ll(resid.numel()),
+    _run("residual_add", lib().bf_residual_add, _ptr(resid), _ptr(delta), _c_ll(resid.numel()),
                                  _c_int(_dtype_code(delta)), _stream())
-    _check(code, "residual_add")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -114,9 +142,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     T, I = out.shape
     if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or gate_up.dtype != out.dtype:
         raise KernelError("silu_mul: gate_up must be contiguous [T, 2*I] of the output's dtype")
-    code = lib().bf_silu_mul(_ptr(gate_up), _ptr(out), _c_int(T), _c_int(I),
+    _run("silu_mul", lib().bf_silu_mul, _ptr(gate_up), _ptr(out), _c_int(T), _c_int(I),
                              _c_int(_dtype_code(out)), _stream())
-    _check(code, "silu_mul")
 
 
 # ------------------------------------------------------------------- attention
@@ -136,12 +163,11 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_w: Optional[torch.Tensor],
     num_slots = k_cache.shape[0] * page_size if k_cache is not None else 0
     if k_cache is not None and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise KernelError("cache pages must be contiguous")
-    code = lib().bf_qk_norm_rope_kv_write(
+    _run("qk_norm_rope_kv_write", lib().bf_qk_norm_rope_kv_write, 
         _ptr(qkv), _c_ll(qkv.stride(0)), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _c_int(rot_half),
         _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(T),
         _c_int(nh), _c_int(nkv if k_cache is not None else 0), _c_int(d), _c_int(page_size),
         _c_ll(num_slots), _c_float(eps), _c_int(_dtype_code(qkv)), _ptr(err), _stream())
-    _check(code, "qk_norm_rope_kv_write")
 
 
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -152,12 +178,11 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     T = q.shape[0]
     if d > 256:
         raise KernelError(f"attention: head_dim {d} is not supported (at most 256)")
-    code = lib().bf_paged_attention_generic(
+    _run("paged_attention_generic", lib().bf_paged_attention_generic, 
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_of_token), _ptr(positions),
         _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(T), _c_int(nh),
         _c_int(nkv), _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
         _c_int(window or 0), _c_float(scale), _c_int(_dtype_code(q)), _ptr(err), _stream())
-    _check(code, "paged_attention_generic")
 
 
 # ------------------------------------------------------------- matrix products
@@ -171,19 +196,17 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if w.shape[1] != K or out.shape != (M, N):
         raise KernelError(f"sgemm_nt: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> "
                           f"{tuple(out.shape)} do not agree")
-    code = lib().bf_sgemm_nt(_ptr(a), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K),
+    _run("sgemm_nt", lib().bf_sgemm_nt, _ptr(a), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K),
                              _c_ll(a.stride(0)), _c_ll(w.stride(0)), _c_ll(out.stride(0)),
                              _stream())
-    _check(code, "sgemm_nt")
 
 
 # -------------------------------------------------------------------- sampling
 def repetition_penalty(logits: torch.Tensor, items: torch.Tensor, penalty: torch.Tensor) -> None:
     """items: int32 [n, 3] of (row, token, count)."""
     _want(logits, torch.float32, "logits"); _want(items, torch.int32, "items")
-    code = lib().bf_repetition_penalty(_ptr(logits), _c_int(logits.shape[1]), _ptr(items),
+    _run("repetition_penalty", lib().bf_repetition_penalty, _ptr(logits), _c_int(logits.shape[1]), _ptr(items),
                                        _c_int(items.shape[0]), _ptr(penalty), _stream())
-    _check(code, "repetition_penalty")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
@@ -192,6 +215,5 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _want(top_k, torch.int32, "top_k"); _want(top_p, torch.float32, "top_p")
     _want(uniform, torch.float32, "uniform"); _want(out, torch.int32, "out")
     R, V = logits.shape
-    code = lib().bf_sample(_ptr(logits), _c_int(R), _c_int(V), _ptr(temperature), _ptr(top_k),
+    _run("sample", lib().bf_sample, _ptr(logits), _c_int(R), _c_int(V), _ptr(temperature), _ptr(top_k),
                            _ptr(top_p), _ptr(uniform), _ptr(out), _stream())
-    _check(code, "sample")

@@ -1,0 +1,161 @@
+"""The Python entry point: ``Engine(model).generate(prompt_ids, ...)``.
+
+Option names follow the reference's engine options and generate call
+(src/engine/batched_engine.ts:3224-3240: ``maxKvMemoryGB`` 10, ``maxSeqLen`` 4096,
+``maxBatchSize`` 64, ``cudaGraphs``; :3133-3203: ``generate(ids, maxNewTokens,
+onToken, sampling)`` returns the generated ids, the stop token included, and stops
+early when the callback returns false).  Unlike the reference's ``generate``, which
+serves one request and reserves pages for prompt + max tokens at once (:3144), any
+number of prompts run together under the continuous-batching scheduler.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Callable, Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import load_config
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .loading import make_env, model_from_dir, model_from_seed
+from .runner import ModelRunner, StepItem
+from .scheduler import FINISHED, Request, Scheduled, Scheduler
+
+
+class Engine:
+    def __init__(self, model: Union[str, object], dtype: str = "bfloat16", *,
+                 random_seed: Optional[int] = None, random_std: float = 0.02,
+                 max_kv_memory_gb: float = 10.0, num_pages: Optional[int] = None,
+                 page_size: int = 16, max_seq_len: int = 4096, max_batch_size: int = 64,
+                 max_tokens_per_step: int = 2048, cuda_graphs: bool = True,
+                 device: str = "cuda:0"):
+        """``model``: a folder with config.json and safetensors, or (with
+        ``random_seed``) a typed configuration whose weights are drawn on the device."""
+        self.env = make_env(dtype, device)
+        if isinstance(model, str):
+            self.config = load_config(model)
+            self.model = model_from_dir(model, self.env)
+        else:
+            if random_seed is None:
+                raise ValueError("a configuration without a folder needs random_seed")
+            self.config = model
+            self.model = model_from_seed(model, self.env, random_seed, std=random_std)
+        self.spec = self.model.spec
+        self.max_seq_len = int(max_seq_len)
+        kv_needs = self.model.kv_needs()
+        if num_pages is None:
+            esize = 2 if self.env.dtype == torch.bfloat16 else 4
+            per_page = sum(2 * n.num_kv_heads * n.head_dim * page_size * esize
+                           for n in kv_needs if n is not None)
+            num_pages = max(1, int(max_kv_memory_gb * (1 << 30)) // max(per_page, 1))
+        cache = CacheManager(kv_needs, self.model.state_needs(), page_size=page_size,
+                             num_pages=num_pages, max_requests=max_batch_size)
+        self.runner = ModelRunner(self.model, cache, self.env)
+        self.scheduler = Scheduler(cache, max_running=max_batch_size,
+                                   max_tokens_per_step=max_tokens_per_step,
+                                   max_model_len=max_seq_len)
+        self.sampler = Sampler(self.env.device)
+        self.cuda_graphs = bool(cuda_graphs)
+        if self.cuda_graphs:
+            self.runner.enable_decode_graphs(max_batch=max_batch_size, max_seq_len=max_seq_len)
+        self._ids = itertools.count()
+        self.requests: Dict[Hashable, Request] = {}
+        self.tokens_prefilled = 0
+        self.tokens_decoded = 0
+        self.step_ms: List[float] = []
+
+    # ---------------------------------------------------------------- requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    rid: Optional[Hashable] = None, eos_ids: Optional[Sequence[int]] = None
+                    ) -> Hashable:
+        rid = next(self._ids) if rid is None else rid
+        eos = tuple(self.spec.eos_token_ids) if eos_ids is None else tuple(eos_ids)
+        bad = [t for t in prompt if not 0 <= int(t) < self.spec.vocab_size]
+        if bad:
+            raise ValueError(f"prompt token ids outside the vocabulary "
+                             f"(0..{self.spec.vocab_size - 1}): {bad[:8]}")
+        req = Request(rid, [int(t) for t in prompt], params or SamplingParams(), eos_ids=eos)
+        self.scheduler.add(req)
+        self.requests[rid] = req
+        return rid
+
+    def abort(self, rid: Hashable) -> None:
+        self.scheduler.abort(self.requests[rid])
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # -------------------------------------------------------------------- step
+    def step(self) -> List[Request]:
+        """One scheduler iteration: plan, run one mixed batch, sample, record.
+        Returns the requests that produced a token in this step."""
+        t0 = time.perf_counter()
+        plan, dropped = self.scheduler.schedule()
+        if not plan:
+            return []
+        items = [StepItem(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.sample else [])
+                 for s in plan]
+        logits = self.runner.step(items)
+        sampling = [s for s in plan if s.sample]
+        ids: List[int] = []
+        if sampling:
+            ids = self.sampler.sample(
+                logits, [s.request.params for s in sampling],
+                [len(s.request.output) for s in sampling],
+                [s.request.output for s in sampling])
+        self.runner.check_errors()
+        for s in plan:
+            if len(s.tokens) > 1 or not s.request.output:
+                self.tokens_prefilled += len(s.tokens)
+            else:
+                self.tokens_decoded += 1
+        self.scheduler.update(plan, ids)
+        self.step_ms.append((time.perf_counter() - t0) * 1e3)
+        return [s.request for s in sampling]
+
+    # ---------------------------------------------------------------- generate
+    def generate(self, prompts, max_tokens: int = 100, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, repetition_penalty: float = 1.0,
+                 seed: Optional[int] = None, eos_ids: Optional[Sequence[int]] = None,
+                 ignore_eos: bool = False,
+                 on_token: Optional[Callable[[int, int], Optional[bool]]] = None):
+        """Generate for one prompt (a list of token ids -> a list of ids) or several
+        (a list of lists -> a list of lists).  The stop token is kept in the output.
+        ``on_token(index_of_prompt, token)`` may return ``False`` to stop that request."""
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        batch = [prompts] if single else list(prompts)
+        rids = []
+        for i, p in enumerate(batch):
+            params = SamplingParams(
+                temperature=temperature, top_k=top_k, top_p=top_p,
+                repetition_penalty=repetition_penalty,
+                seed=None if seed is None else seed + i, max_tokens=max_tokens,
+                ignore_eos=ignore_eos)
+            rids.append(self.add_request(p, params, eos_ids=eos_ids))
+        index = {rid: i for i, rid in enumerate(rids)}
+        while any(self.requests[r].state != FINISHED for r in rids):
+            for req in self.step():
+                if on_token is not None and req.rid in index:
+                    if on_token(index[req.rid], req.output[-1]) is False:
+                        self.abort(req.rid)
+        outs = [self.requests.pop(r).output for r in rids]
+        return outs[0] if single else outs
+
+    # ------------------------------------------------------------------- stats
+    def stats(self) -> dict:
+        """Pages, queues and token counts (the reference: src/engine/batched_engine.ts:2993)."""
+        cache = self.runner.cache
+        return {
+            "pages_total": [g.pool.num_pages for g in cache.groups],
+            "pages_free": cache.num_free_pages(),
+            "running": len(self.scheduler.running),
+            "waiting": len(self.scheduler.waiting),
+            "tokens_prefilled": self.tokens_prefilled,
+            "tokens_decoded": self.tokens_decoded,
+            "preemptions": self.scheduler.num_preemptions,
+            "steps": self.runner.steps,
+            "kernel_launches": __import__("binfer_b200.csrc.ops", fromlist=["x"]).launches(),
+        }

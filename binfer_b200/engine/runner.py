@@ -102,20 +102,34 @@ class ModelRunner:
             off += B * w
         return fields, off
 
-    def build_context(self, items: Sequence[StepItem]) -> StepContext:
-        """Describe ``items`` to the device.  Pages must already be reserved."""
+    def build_context(self, items: Sequence[StepItem], pad_to: Optional[int] = None,
+                      widths: Optional[Sequence[int]] = None,
+                      dev: Optional[torch.Tensor] = None) -> StepContext:
+        """Describe ``items`` to the device.  Pages must already be reserved.
+
+        ``pad_to`` (single-token items only) pads the batch with rows that belong to
+        no request: token 0 at position 0, writing to and reading from the scratch
+        page.  ``widths`` fixes the block tables' widths and ``dev`` the device buffer,
+        so that a captured graph finds every field at the same address each time.
+        """
         cache = self.cache
-        B = len(items)
-        q_lens = [len(it.tokens) for it in items]
+        n_real = len(items)
+        B = pad_to or n_real
+        q_lens = [len(it.tokens) for it in items] + [1] * (B - n_real)
         T = sum(q_lens)
         rcs = [cache.get(it.rid) for it in items]
-        starts = [rc.length for rc in rcs]
+        starts = [rc.length for rc in rcs] + [0] * (B - n_real)
         ctx_lens = [s + n for s, n in zip(starts, q_lens)]
-        R = sum(len(it.want) for it in items)
-        widths = [max(1, max(len(rc.tables[g.index]) for rc in rcs)) for g in cache.groups]
+        if pad_to:
+            R = B                               # every row's logits; the caller picks
+        else:
+            R = sum(len(it.want) for it in items)
+        if widths is None:
+            widths = [max(1, max(len(rc.tables[g.index]) for rc in rcs)) for g in cache.groups]
         fields, total = self._layout(T, B, R, widths)
         host, ring = self._staging.take(total)
         h = host.numpy()
+        h[:total] = 0
 
         def view(name):
             a, n = fields[name]
@@ -130,31 +144,40 @@ class ModelRunner:
             pos[t:t + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
             sot[t:t + n] = b
             qs[b] = t
-            for w in it.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"request {it.rid!r}: wanted place {w} is outside its "
-                                     f"{n} tokens of this step")
-                rows[r] = t + w
-                r += 1
+            if not pad_to:
+                for w in it.want:
+                    if not 0 <= w < n:
+                        raise ValueError(f"request {it.rid!r}: wanted place {w} is outside "
+                                         f"its {n} tokens of this step")
+                    rows[r] = t + w
+                    r += 1
             t += n
+        for b in range(n_real, B):              # padding rows
+            sot[b] = b
+            qs[b] = b
         qs[B] = T
+        if pad_to:
+            rows[:] = np.arange(B, dtype=np.int32)
         view("ctx_lens")[:] = ctx_lens
-        view("state_slots")[:] = [rc.slot for rc in rcs]
+        view("state_slots")[:n_real] = [rc.slot for rc in rcs]
         for g in cache.groups:
             w, ps = widths[g.index], g.page_size
             sl = view(f"slots{g.index}")
             tb = view(f"tables{g.index}").reshape(B, w)
-            tb[:] = 0
             t = 0
             for b, rc in enumerate(rcs):
                 table = np.asarray(rc.tables[g.index], dtype=np.int32)
+                if len(table) > w:
+                    raise ValueError(f"request {rc.rid!r} holds {len(table)} pages, the "
+                                     f"block table has room for {w}")
                 tb[b, :len(table)] = table
                 p = np.arange(starts[b], ctx_lens[b])
                 sl[t:t + q_lens[b]] = table[p // ps] * ps + p % ps
                 t += q_lens[b]
 
-        dev = torch.empty(total, dtype=torch.int32, device=self.env.device)
-        dev.copy_(host[:total], non_blocking=True)
+        if dev is None:
+            dev = torch.empty(total, dtype=torch.int32, device=self.env.device)
+        dev[:total].copy_(host[:total], non_blocking=True)
         self._staging.sent(ring)
         self.h2d_bytes += total * 4
 
@@ -200,12 +223,69 @@ class ModelRunner:
         self.reserve(items)
         for it in items:
             self.cache.zero_fresh_state(self.cache.get(it.rid))
-        ctx = self.build_context(items)
-        logits = self.model.forward(ctx, self.views)
-        for it, new_len in zip(items, ctx.ctx_lens_host):
+        new_lens = [self.cache.get(it.rid).length + len(it.tokens) for it in items]
+        if self._can_replay(items, new_lens):
+            logits = self._graph_step(items)
+        else:
+            ctx = self.build_context(items)
+            logits = self.model.forward(ctx, self.views)
+        for it, new_len in zip(items, new_lens):
             self.cache.commit(it.rid, new_len)
         self.steps += 1
         return logits
+
+    # ------------------------------------------------------- captured decoding
+    def enable_decode_graphs(self, max_batch: int = 64, max_seq_len: int = 4096) -> None:
+        """Replay steps that hold only single tokens from CUDA graphs, one graph per
+        batch-size bucket (1, 2, 4, ... up to ``max_batch``), captured at first use.
+
+        The reference captures decode only for batches up to 8 and relies on its
+        allocator handing back the same addresses (src/engine/batched_engine.ts:1790,
+        2152-2164); its padded rows write into block 0 of a live request (:2060-2078).
+        Here every input sits in a fixed buffer per bucket, and padded rows use the
+        scratch page.  The returned logits are a view of the graph's output buffer:
+        they are valid until the next step of the same bucket.
+        """
+        buckets = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b < max_batch]
+        self._buckets = sorted(set(buckets + [int(max_batch)]))
+        self._graph_seq_len = int(max_seq_len)
+        self._graphs = {}
+
+    def _can_replay(self, items: Sequence[StepItem], new_lens: Sequence[int]) -> bool:
+        return (getattr(self, "_buckets", None) is not None
+                and len(items) <= self._buckets[-1]
+                and all(len(it.tokens) == 1 for it in items)
+                and max(new_lens) <= self._graph_seq_len)
+
+    def _graph_step(self, items: Sequence[StepItem]) -> torch.Tensor:
+        B = len(items)
+        bucket = next(b for b in self._buckets if b >= B)
+        widths = [-(-self._graph_seq_len // g.page_size) for g in self.cache.groups]
+        st = self._graphs.get(bucket)
+        if st is None:
+            _, total = self._layout(bucket, bucket, bucket, widths)
+            st = {"dev": torch.zeros(total, dtype=torch.int32, device=self.env.device),
+                  "graph": None, "logits": None}
+            self._graphs[bucket] = st
+        ctx = self.build_context(items, pad_to=bucket, widths=widths, dev=st["dev"])
+        ctx.max_ctx_len = self._graph_seq_len     # launch shapes must not follow the batch
+        if st["graph"] is None:
+            logits = self.model.forward(ctx, self.views)      # this step's result, eagerly
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                st["logits"] = self.model.forward(ctx, self.views)
+            st["graph"] = graph
+            self.graph_captures = getattr(self, "graph_captures", 0) + 1
+        else:
+            st["graph"].replay()
+            logits = st["logits"]
+            self.graph_replays = getattr(self, "graph_replays", 0) + 1
+        rows = [b for b, it in enumerate(items) if len(it.want) > 0]
+        if len(rows) == B:
+            return logits[:B]
+        return logits[torch.tensor(rows, dtype=torch.long, device=self.env.device)] \
+            if rows else logits[:0]
 
     def check_errors(self) -> None:
         """Raise if a kernel flagged bad input since the last check (synchronises)."""

@@ -26,11 +26,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         return out
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
+    prof = ops._profiler
+    if prof is not None:
+        prof.begin("cublas_gemm_bf16")
+    ops.count_library_launch()
     if out_dtype == torch.float32:
         if out is None:
             out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
-        return out
-    if out is None:
-        return torch.mm(x, w.t())
-    return torch.mm(x, w.t(), out=out)
+    elif out is None:
+        out = torch.mm(x, w.t())
+    else:
+        torch.mm(x, w.t(), out=out)
+    if prof is not None:
+        prof.end("cublas_gemm_bf16")
+    return out

@@ -1,0 +1,55 @@
+"""Sampling on the device from the step's float32 logits.
+
+The reference copies the whole vocabulary of logits to the host for every token
+and samples there (src/engine/sampler.ts:57-157; the copy:
+src/engine/batched_engine.ts:2282-2283).  Here the penalty, the filters and the
+draw run in one kernel per row, and only the chosen ids come back.
+"""
+from __future__ import annotations
+
+from collections import Counter
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .params import SamplingParams, uniform
+
+
+class Sampler:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.d2h_bytes = 0
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               draw_index: Sequence[int], generated: Sequence[Sequence[int]]) -> List[int]:
+        """One token per row of ``logits [R, V]``.  ``draw_index[r]`` is how many tokens
+        request r has drawn so far; ``generated[r]`` feeds the repetition penalty."""
+        R = logits.shape[0]
+        assert R == len(params) == len(draw_index) == len(generated)
+        out = self.sample_async(logits, params, draw_index, generated)
+        ids = out.cpu()
+        self.d2h_bytes += R * 4
+        return ids.tolist()
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                     draw_index: Sequence[int], generated: Sequence[Sequence[int]]) -> torch.Tensor:
+        R = logits.shape[0]
+        host = np.empty((5, R), dtype=np.float32)
+        host[0] = [p.temperature for p in params]
+        host[1] = [p.top_p for p in params]
+        host[2] = [uniform(p.seed, n) if not p.greedy else 0.0
+                   for p, n in zip(params, draw_index)]
+        host[3] = [p.repetition_penalty for p in params]
+        host[4].view(np.int32)[:] = [p.top_k for p in params]
+        dev = torch.from_numpy(host).to(self.device, non_blocking=False)
+        if any(p.repetition_penalty != 1.0 for p in params):
+            items = [(r, tok, cnt) for r, (p, g) in enumerate(zip(params, generated))
+                     if p.repetition_penalty != 1.0 for tok, cnt in Counter(g).items()]
+            if items:
+                it = torch.tensor(items, dtype=torch.int32).to(self.device)
+                ops.repetition_penalty(logits, it, dev[3])
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        ops.sample(logits, dev[0], dev[4].view(torch.int32), dev[1], dev[2], out)
+        return out
