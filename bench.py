@@ -1,0 +1,308 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens per second of the Qwen3-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Default run: the layer sizes of the Qwen3-8B shape with random weights in
+bfloat16, a batch of 8 requests decoding at a context of 4096 tokens.  A "step"
+is one decode step (one new token per request).  One JSON line is printed with
+
+- ``value``: decoded tokens per second, timed on the device with CUDA events
+  around exactly K steps after W warm-up steps (the step replays the engine's
+  CUDA graph; token ids are fed from the host, nothing is read back);
+- ``e2e``: the same through the Python entry point (``Engine.step``: scheduler,
+  pinned host-to-device copy of the step's inputs, device sampling, read-back of
+  the sampled ids each step);
+- ``prefill``: one step over a 2,048-token prompt, with its fraction of the
+  measured bf16 peak;
+- ``roofline``: bytes the decode step must read (every weight once, the cache of
+  the live requests) over its time, against the measured copy bandwidth;
+- ``points``: decode tokens per second at batch 1 and 64;
+- ``clocks``: SM clock and throttle reasons sampled during the timed region.
+
+Between timed steps the inputs (15 GB of weights, gigabytes of cache) are far
+larger than the 126 MB L2, so no explicit flush is needed.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36,
+    hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+    tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu",
+    attention_bias=False, use_sliding_window=False)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while running."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self):
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, a=0, b=None):
+        rows = self.rows[a:b] or self.rows
+        sm = [float(r[0]) for r in rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) > 3 + i and r[3 + i] == "Active" for r in rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(rows)}
+
+
+def reference_arm():
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "bwasti/binfer is a Bun/TypeScript program (no setup.py or pyproject.toml: "
+                       "pip reports 'not installable'); Bun is not installed and cannot be "
+                       "installed offline, and its CMake build pins sm_90"}))
+    return 0
+
+
+def fill_cache(engine, runner, n_req, length, vocab, gen):
+    """n_req live requests holding ``length`` tokens each, prefilled through the step function."""
+    import torch
+    from binfer_b200.engine.runner import StepItem
+    rids = []
+    for i in range(n_req):
+        rid = f"bench{i}"
+        runner.add_request(rid)
+        toks = torch.randint(0, vocab, (length,), generator=gen).tolist()
+        for a in range(0, length, 2048):
+            runner.step([StepItem(rid, toks[a:a + 2048], [])])
+        rids.append(rid)
+    torch.cuda.synchronize()
+    return rids
+
+
+def time_decode(runner, sampler, rids, vocab, steps, warmup, gen, clocks=None):
+    """Device time of ``steps`` decode steps (graph replay + greedy sampling)."""
+    import torch
+    from binfer_b200.csrc import ops
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.sampling import SamplingParams
+    B = len(rids)
+    params = [SamplingParams(temperature=0.0, seed=0) for _ in rids]
+    toks = torch.randint(0, vocab, (steps + warmup, B), generator=gen).tolist()
+
+    def one(i):
+        logits = runner.step([StepItem(r, [toks[i][b]], [0]) for b, r in enumerate(rids)])
+        return sampler.sample_async(logits, params, [0] * B, [[]] * B)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    a = clocks.mark() if clocks else 0
+    l0 = ops.launches()
+    g0 = getattr(runner, "graph_kernel_launches", 0)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    end.record()
+    torch.cuda.synchronize()
+    b = clocks.mark() if clocks else 0
+    ms = start.elapsed_time(end)
+    launches = (ops.launches() - l0) + (getattr(runner, "graph_kernel_launches", 0) - g0)
+    return ms / steps, launches, (a, b)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from binfer_b200 import Engine, Qwen3Config
+    from binfer_b200.csrc import ops
+    from binfer_b200.engine.runner import StepItem
+
+    peaks = load_peaks()
+    raw = dict(QWEN3_8B)
+    full_layers = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = Qwen3Config.from_dict(raw)
+    steps, warmup, B = args.steps, args.warmup, args.batch
+    max_b = max(B, 1 if args.no_points else 64)
+    pages = max_b * (CONTEXT // PAGE_SIZE) + 64
+    t0 = time.time()
+    engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=pages, page_size=PAGE_SIZE,
+                    max_seq_len=CONTEXT, max_batch_size=max_b, max_tokens_per_step=2048,
+                    cuda_graphs=True)
+    runner, sampler = engine.runner, engine.sampler
+    vocab = cfg.vocab_size
+    gen = torch.Generator().manual_seed(0)
+    load_s = time.time() - t0
+
+    weight_bytes = engine.model.weight_bytes() - engine.model.embed.numel() * 2 * (
+        0 if cfg.tie_word_embeddings else 1)
+    kv_per_token = cfg.kv_bytes_per_token(2)
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    def decode_point(batch, n_steps, n_warm):
+        start_len = CONTEXT - (n_steps + n_warm)
+        rids = fill_cache(engine, runner, batch, start_len, vocab, gen)
+        ms, launches, span = time_decode(runner, sampler, rids, vocab, n_steps, n_warm, gen, clocks)
+        mean_ctx = start_len + n_warm + n_steps / 2
+        for r in rids:
+            runner.free_request(r)
+        return ms, launches, span, mean_ctx
+
+    # ---- the headline: batch B at context 4096
+    ms_step, launches, span, mean_ctx = decode_point(B, steps, warmup)
+    value = B / (ms_step / 1e3)
+    bytes_step = weight_bytes + B * mean_ctx * kv_per_token
+    achieved = bytes_step / (ms_step / 1e3) / 1e9
+    clk = clocks.summary(*span)
+
+    # ---- end to end through the entry point: scheduler, H2D inputs, D2H ids every step
+    prompts = [torch.randint(0, vocab, (CONTEXT - (steps + warmup) - 1,), generator=gen).tolist()
+               for _ in range(B)]
+    from binfer_b200.sampling import SamplingParams
+    for p in prompts:
+        engine.add_request(p, SamplingParams(max_tokens=steps + warmup + 1, ignore_eos=True,
+                                             seed=0))
+    while any(r.remaining > 1 or not r.output for r in engine.scheduler.running) \
+            or engine.scheduler.waiting:
+        engine.step()                                   # prefill portions
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h0, d0 = runner.h2d_bytes, sampler.d2h_bytes
+    t1 = time.perf_counter()
+    n_e2e = 0
+    for _ in range(steps - 1):
+        n_e2e += len(engine.step())
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t1
+    e2e = {"value": n_e2e / e2e_s, "unit": "tokens/s",
+           "h2d_bytes_per_step": (runner.h2d_bytes - h0) // max(steps - 1, 1),
+           "d2h_bytes_per_step": (sampler.d2h_bytes - d0) // max(steps - 1, 1)}
+    while engine.has_work():
+        engine.step()
+
+    points, prefill = {}, None
+    if not args.no_points:
+        for b in (1, 64):
+            ms_b, _, _, _ = decode_point(b, min(steps, 32), warmup)
+            points[f"decode_b{b}"] = b / (ms_b / 1e3)
+        # ---- prefill of 2,048 tokens in one step
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        times = []
+        for i in range(5):
+            runner.add_request("pf")
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            runner.step([StepItem("pf", toks, [PREFILL_TOKENS - 1])])
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+            runner.free_request("pf")
+        pf_ms = statistics.median(times[2:])
+        L, H, I = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
+        Q, KV = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+        T = PREFILL_TOKENS
+        flops = L * (2 * T * (H * (Q + 2 * KV) + Q * H + 3 * H * I)
+                     + 4 * cfg.num_attention_heads * cfg.head_dim * T * (T + 1) / 2) \
+            + 2 * H * vocab
+        prefill = {"value": T / (pf_ms / 1e3), "tokens": T, "ms": pf_ms,
+                   "frac": flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+    clocks.stop()
+    runner.check_errors()
+
+    out = {
+        "metric": "decode tok/s @ batch 8, context 4096 (Qwen3-8B shape, bf16, 1 B200)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape, random weights", "layers": cfg.num_hidden_layers,
+            "layers_of_full_config": full_layers, "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size, "tied": cfg.tie_word_embeddings, "global_batch": B,
+            "seq_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "1 GPU",
+            "cuda_graphs": True, "l2": "inputs larger than L2 (weights 15 GB per step)",
+            "peaks": peaks["source"],
+        },
+        "clocks": clk,
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"]},
+        "points": points,
+    }
+    if prefill is not None:
+        out["prefill"] = prefill
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,350 @@
+// Split-KV attention for single-token (decode) rows over the paged bf16 cache.
+//
+// Grid (split, kv_head, row).  A CTA takes the 128 keys [split*128, split*128+128)
+// of one request for one kv head, and all query heads of that kv head's group
+// together: the group's heads are the rows of the tensor-core tile, so every key
+// and value byte is read from HBM once per group.  The reference's decode kernel
+// is one block per (sequence, query head), reads each kv head once per query head
+// and never splits the keys across blocks (cuda/kernels/paged_attention.cu:370-489).
+//
+// The whole 128-key K and V tile is fetched with cp.async in one go (64 KB for
+// head size 128); three CTAs fit an SM, so one CTA's math overlaps another's
+// loads.  Scores and P.V run on mma.sync m16n8k16 (bf16 in, float accumulate);
+// softmax is float with exp2 and the scale folded in.  Each of the 4 warps owns 32
+// keys; the warps' (max, sum, out) are merged in shared memory, and the CTA writes
+// an unnormalised partial to scratch memory.  A second kernel merges the splits
+// of a row in ascending order and normalises.  Which keys a warp and a split own
+// depends only on the key's position, so the result for a row does not depend on
+// the rest of the batch.
+//
+// Scratch: part_o float [rows, nh, max_splits, D], part_ml float [rows, nh, max_splits, 2].
+#include <float.h>
+
+#include "common.cuh"
+
+#define DEC_SPLIT 128
+#define DEC_THREADS 128
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem),
+               "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                               unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_attention_split_kernel(const __nv_bfloat16* __restrict__ q,
+                              const __nv_bfloat16* __restrict__ k_cache,
+                              const __nv_bfloat16* __restrict__ v_cache,
+                              const int* __restrict__ rows, const int* __restrict__ seq_of_token,
+                              const int* __restrict__ positions,
+                              const int* __restrict__ block_tables, int table_stride,
+                              float* __restrict__ part_o, float* __restrict__ part_ml, int nh,
+                              int nkv, int page_size, int num_pages, int window, int max_splits,
+                              float scale_log2, int* __restrict__ err) {
+  constexpr int LD = D + 8;            // padded row: ldmatrix rows fall in distinct banks
+  constexpr int CPK = D / 8;           // 16-byte chunks per key
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* Vs = Ks + DEC_SPLIT * LD;
+  long long* rowoff = reinterpret_cast<long long*>(Vs + DEC_SPLIT * LD);
+
+  const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+  const int t = rows ? rows[r] : r;
+  const int p = positions[t];
+  const int j0 = window > 0 ? max(0, p - window + 1) : 0;
+  const int k_begin = split * DEC_SPLIT;
+  if (k_begin > p || k_begin + DEC_SPLIT <= j0) return;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = nh / nkv;
+  const int* table = block_tables + (size_t)seq_of_token[t] * table_stride;
+
+  {  // where each key of the tile lives
+    const int j = k_begin + tid;
+    long long off = -1;
+    if (j >= j0 && j <= p) {
+      const int lp = j / page_size;
+      const int page = table[lp];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(err, BF_ERR_PAGE);
+      } else {
+        off = (((long long)page * nkv + g) * page_size + (j - lp * page_size)) * D;
+      }
+    }
+    rowoff[tid] = off;
+  }
+  __syncthreads();
+  for (int c = tid; c < DEC_SPLIT * CPK; c += DEC_THREADS) {
+    const int key = c / CPK, part = c - key * CPK;
+    const long long off = rowoff[key];
+    cp_async16(Ks + key * LD + part * 8, off >= 0 ? k_cache + off + part * 8 : k_cache,
+               off >= 0 ? 16 : 0);
+  }
+  cp_async_commit();
+  for (int c = tid; c < DEC_SPLIT * CPK; c += DEC_THREADS) {
+    const int key = c / CPK, part = c - key * CPK;
+    const long long off = rowoff[key];
+    cp_async16(Vs + key * LD + part * 8, off >= 0 ? v_cache + off + part * 8 : v_cache,
+               off >= 0 ? 16 : 0);
+  }
+  cp_async_commit();
+
+  const int r0 = lane >> 2, cq = (lane & 3) * 2;
+  const int wkey = warp * 32;          // this warp's first key inside the tile
+  bool first_block = true;
+
+  for (int hb = 0; hb < G; hb += 16) {
+    const int gblk = min(16, G - hb);
+    // query fragments: rows = heads of the group, zero beyond the group
+    unsigned qa[D / 16][4];
+    {
+      const __nv_bfloat16* q0 = q + ((size_t)t * nh + (size_t)g * G + hb + r0) * D;
+      const __nv_bfloat16* q1 = q0 + (size_t)8 * D;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int c = ks * 16 + cq;
+        qa[ks][0] = r0 < gblk ? *reinterpret_cast<const unsigned*>(q0 + c) : 0u;
+        qa[ks][1] = r0 + 8 < gblk ? *reinterpret_cast<const unsigned*>(q1 + c) : 0u;
+        qa[ks][2] = r0 < gblk ? *reinterpret_cast<const unsigned*>(q0 + c + 8) : 0u;
+        qa[ks][3] = r0 + 8 < gblk ? *reinterpret_cast<const unsigned*>(q1 + c + 8) : 0u;
+      }
+    }
+    if (first_block) {
+      cp_async_wait<1>();
+      __syncthreads();                 // every thread's K chunks have landed
+    }
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        unsigned b[4];
+        ldmatrix_x4(b, Ks + (wkey + nt * 8 + (lane & 7)) * LD + ks * 16 + (lane >> 3) * 8);
+        mma_bf16_16816(s[nt], qa[ks], b[0], b[1]);
+        mma_bf16_16816(s[nt], qa[ks + 1], b[2], b[3]);
+      }
+    }
+    // mask, scale, softmax over this warp's 32 keys
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = k_begin + wkey + nt * 8 + cq + (i & 1);
+        s[nt][i] = (j >= j0 && j <= p) ? s[nt][i] * scale_log2 : -INFINITY;
+      }
+      m0 = fmaxf(m0, fmaxf(s[nt][0], s[nt][1]));
+      m1 = fmaxf(m1, fmaxf(s[nt][2], s[nt][3]));
+    }
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+    const float u0 = m0 == -INFINITY ? 0.f : m0, u1 = m1 == -INFINITY ? 0.f : m1;
+    float l0 = 0.f, l1 = 0.f;
+    unsigned pa[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const float e0 = exp2f(s[nt][0] - u0), e1 = exp2f(s[nt][1] - u0);
+      const float e2 = exp2f(s[nt][2] - u1), e3 = exp2f(s[nt][3] - u1);
+      l0 += e0 + e1;
+      l1 += e2 + e3;
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(e0, e1);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e2, e3);
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    if (first_block) {
+      cp_async_wait<0>();
+      __syncthreads();                 // V has landed
+      first_block = false;
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[dn][i] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int dn = 0; dn < D / 8; dn += 2) {
+        unsigned b[4];
+        const int m = lane >> 3;
+        ldmatrix_x4_trans(b, Vs + (wkey + kk * 16 + (m & 1) * 8 + (lane & 7)) * LD +
+                                 (dn + (m >> 1)) * 8);
+        mma_bf16_16816(o[dn], pa[kk], b[0], b[1]);
+        mma_bf16_16816(o[dn + 1], pa[kk], b[2], b[3]);
+      }
+    }
+
+    // merge the four warps' partials in shared memory.  With a single head block the K
+    // tile is dead here (every warp passed the barrier between its score and its P.V
+    // phase), so the merge buffer lies over it; with several head blocks the tiles are
+    // read again, and the buffer sits behind them.
+    float* red = G <= 16 ? reinterpret_cast<float*>(Ks)
+                         : reinterpret_cast<float*>(rowoff + DEC_SPLIT);
+    float* red_m = red;                       // [4][16]
+    float* red_l = red + 64;                  // [4][16]
+    float* red_o = red + 128;                 // [4][16][D]
+    if ((lane & 3) == 0) {
+      red_m[warp * 16 + r0] = m0;
+      red_m[warp * 16 + r0 + 8] = m1;
+      red_l[warp * 16 + r0] = l0;
+      red_l[warp * 16 + r0 + 8] = l1;
+    }
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn) {
+      float* o0 = red_o + ((size_t)warp * 16 + r0) * D + dn * 8 + cq;
+      float* o1 = o0 + (size_t)8 * D;
+      o0[0] = o[dn][0];
+      o0[1] = o[dn][1];
+      o1[0] = o[dn][2];
+      o1[1] = o[dn][3];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < gblk * D; idx += DEC_THREADS) {
+      const int row = idx / D, col = idx - row * D;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 16 + row]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = red_m[w * 16 + row];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+        L += red_l[w * 16 + row] * f;
+        O += red_o[((size_t)w * 16 + row) * D + col] * f;
+      }
+      const size_t base = ((size_t)r * nh + (size_t)g * G + hb + row) * max_splits + split;
+      part_o[base * D + col] = O;
+      if (col == 0) {
+        part_ml[base * 2] = M;
+        part_ml[base * 2 + 1] = L;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Merge the splits of each (row, head) in ascending order and normalise.
+template <int D>
+__global__ void decode_attention_merge_kernel(const float* __restrict__ part_o,
+                                              const float* __restrict__ part_ml,
+                                              const int* __restrict__ rows,
+                                              const int* __restrict__ positions,
+                                              __nv_bfloat16* __restrict__ out, int nh, int window,
+                                              int max_splits) {
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int t = rows ? rows[r] : r;
+  const int p = positions[t];
+  const int j0 = window > 0 ? max(0, p - window + 1) : 0;
+  const int s_first = j0 / DEC_SPLIT, s_last = p / DEC_SPLIT;
+  const size_t base = ((size_t)r * nh + h) * max_splits;
+  float M = -INFINITY;
+  for (int s = s_first; s <= s_last; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float L = 0.f;
+  for (int s = s_first; s <= s_last; ++s)
+    L += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - M);
+  const float inv = 1.f / L;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = s_first; s <= s_last; ++s)
+      acc += part_o[(base + s) * D + c] * exp2f(part_ml[(base + s) * 2] - M);
+    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int D>
+static int launch_decode(const void* q, const void* k_cache, const void* v_cache, const int* rows,
+                         const int* seq_of_token, const int* positions, const int* block_tables,
+                         int table_stride, void* out, float* part_o, float* part_ml, int n_rows,
+                         int nh, int nkv, int page_size, int num_pages, int window,
+                         int max_splits, float scale, int* err, cudaStream_t stream) {
+  constexpr int LD = D + 8;
+  const size_t tiles = (size_t)2 * DEC_SPLIT * LD * 2 + DEC_SPLIT * 8;
+  const size_t merge = (size_t)(128 + 4 * 16 * D) * 4;
+  const size_t smem_max = tiles + merge;
+  const size_t smem = nh / nkv <= 16 ? tiles : smem_max;
+  auto kern = decode_attention_split_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_max);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(max_splits, nkv, n_rows);
+  kern<<<grid, DEC_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, rows,
+      seq_of_token, positions, block_tables, table_stride, part_o, part_ml, nh, nkv, page_size,
+      num_pages, window, max_splits, scale * 1.4426950408889634f, err);
+  int e = bf_launch_status();
+  if (e) return e;
+  decode_attention_merge_kernel<D><<<dim3(n_rows, nh), D >= 128 ? 128 : 64, 0, stream>>>(
+      part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);
+  return bf_launch_status();
+}
+
+// max_splits must be >= ceil(longest context / 128) of the rows given.
+// Returns cudaErrorInvalidValue for head sizes it does not take (take the generic kernel).
+BF_EXPORT int bf_decode_attention(const void* q, const void* k_cache, const void* v_cache,
+                                  const int* rows, const int* seq_of_token, const int* positions,
+                                  const int* block_tables, int table_stride, void* out,
+                                  float* part_o, float* part_ml, int n_rows, int nh, int nkv,
+                                  int d, int page_size, int num_pages, int window, int max_splits,
+                                  float scale, int* err, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+#define BF_DEC_CASE(DD)                                                                         \
+  case DD:                                                                                      \
+    return launch_decode<DD>(q, k_cache, v_cache, rows, seq_of_token, positions, block_tables,  \
+                             table_stride, out, part_o, part_ml, n_rows, nh, nkv, page_size,    \
+                             num_pages, window, max_splits, scale, err, stream)
+  switch (d) {
+    BF_DEC_CASE(32);
+    BF_DEC_CASE(64);
+    BF_DEC_CASE(96);
+    BF_DEC_CASE(128);
+    BF_DEC_CASE(256);
+    default:
+      return (int)cudaErrorInvalidValue;
+  }
+#undef BF_DEC_CASE
+}
+
+BF_EXPORT int bf_decode_attention_split_keys() { return DEC_SPLIT; }

@@ -185,6 +185,35 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _c_int(window or 0), _c_float(scale), _c_int(_dtype_code(q)), _ptr(err), _stream())
 
 
+DECODE_HEAD_DIMS = (32, 64, 96, 128, 256)
+DECODE_SPLIT_KEYS = 128
+
+
+def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     rows: Optional[torch.Tensor], n_rows: int, seq_of_token: torch.Tensor,
+                     positions: torch.Tensor, block_tables: torch.Tensor, out: torch.Tensor,
+                     nh: int, nkv: int, d: int, window: Optional[int], scale: float,
+                     max_ctx_len: int, err: torch.Tensor) -> None:
+    """Split-KV attention for rows that bring one token each (bfloat16 only).
+
+    ``rows`` lists the token rows to run (None: rows 0..n_rows-1); ``max_ctx_len``
+    bounds the context of every such row.  Scratch for the splits' partial results
+    is taken from torch's allocator."""
+    if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
+        raise KernelError(f"decode_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
+    max_splits = max(1, -(-int(max_ctx_len) // DECODE_SPLIT_KEYS))
+    part_o = torch.empty((n_rows, nh, max_splits, d), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n_rows, nh, max_splits, 2), dtype=torch.float32, device=q.device)
+    _run("decode_attention", lib().bf_decode_attention,
+         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(rows), _ptr(seq_of_token), _ptr(positions),
+         _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _ptr(part_o),
+         _ptr(part_ml), _c_int(n_rows), _c_int(nh), _c_int(nkv), _c_int(d),
+         _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]), _c_int(window or 0),
+         _c_int(max_splits), _c_float(scale), _ptr(err), _stream())
+    global _launches
+    _launches += 1          # two kernels: the splits and their merge
+
+
 # ------------------------------------------------------------- matrix products
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic."""

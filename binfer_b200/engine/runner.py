@@ -272,14 +272,19 @@ class ModelRunner:
         if st["graph"] is None:
             logits = self.model.forward(ctx, self.views)      # this step's result, eagerly
             torch.cuda.synchronize()
+            from ..csrc import ops
             graph = torch.cuda.CUDAGraph()
+            before = ops.launches()
             with torch.cuda.graph(graph):
                 st["logits"] = self.model.forward(ctx, self.views)
             st["graph"] = graph
+            st["own_kernels"] = ops.launches() - before     # this library's kernels per replay
             self.graph_captures = getattr(self, "graph_captures", 0) + 1
         else:
             st["graph"].replay()
             logits = st["logits"]
+            self.graph_kernel_launches = (getattr(self, "graph_kernel_launches", 0)
+                                          + st["own_kernels"])
             self.graph_replays = getattr(self, "graph_replays", 0) + 1
         rows = [b for b, it in enumerate(items) if len(it.want) > 0]
         if len(rows) == B:

@@ -91,11 +91,24 @@ class GQAAttention(Mixer):
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext,
                view: EntryView) -> None:
+        """Attention of every token row over its request's pages.
+
+        float32: the generic kernel, whose sums have one fixed order per position.
+        bfloat16: rows that bring a single token go to the split-KV decode kernel;
+        the rest (and head sizes the tuned kernels do not take) to the generic one.
+        """
         s = self.spec
+        tables = ctx.block_tables[view.group]
+        fast = q.dtype == torch.bfloat16 and s.head_dim in ops.DECODE_HEAD_DIMS
+        if fast and ctx.decode_only:
+            ops.decode_attention(
+                q, view.k_cache, view.v_cache, None, ctx.T, ctx.seq_of_token, ctx.positions,
+                tables, out, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale,
+                ctx.max_ctx_len, ctx.err)
+            return
         ops.paged_attention_generic(
-            q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions,
-            ctx.block_tables[view.group], out, s.num_heads, s.num_kv_heads, s.head_dim,
-            s.window, s.softmax_scale, ctx.err)
+            q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, tables, out,
+            s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale, ctx.err)
 
 
 register_mixer("attention", GQAAttention)

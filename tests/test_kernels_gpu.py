@@ -1,0 +1,293 @@
+"""Each CUDA kernel alone against a plain float64 reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+BF16, F32 = torch.bfloat16, torch.float32
+TOL = {F32: 2e-6, BF16: 1.2e-2}     # relative to the largest reference magnitude
+
+
+def _close(got, ref, dtype, scale=1.0):
+    err = float((got.double().cpu() - ref.double().cpu()).abs().max())
+    mag = float(ref.double().abs().max()) or 1.0
+    assert err <= TOL[dtype] * scale * mag, f"error {err:.3g} vs magnitude {mag:.3g}"
+
+
+def _err(dev):
+    return torch.zeros(1, dtype=torch.int32, device=dev)
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_embed_gather(cuda_device, dtype):
+    from binfer_b200.csrc import ops
+    table = torch.randn(301, 100, device=cuda_device).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=cuda_device)
+    out = torch.empty(5, 100, device=cuda_device)
+    err = _err(cuda_device)
+    ops.embed_gather(table, ids, out, 1.0, err)
+    assert torch.equal(out, table.float()[ids.long()])
+    assert int(err.item()) == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=cuda_device)
+    out2 = torch.ones(2, 100, device=cuda_device)
+    ops.embed_gather(table, bad, out2, 1.0, err)
+    assert int(err.item()) == 1 and float(out2[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H", [100, 1536, 5000])
+def test_add_rmsnorm(cuda_device, dtype, H):
+    from binfer_b200.csrc import ops
+    resid = torch.randn(9, H, device=cuda_device)
+    delta = torch.randn(9, H, device=cuda_device).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, device=cuda_device)
+    r0 = resid.clone()
+    out = torch.empty(9, H, device=cuda_device, dtype=dtype)
+    ops.add_rmsnorm(resid, delta, w, out, 1e-5)
+    x = r0.double() + delta.double()
+    _close(resid, x, F32)
+    _close(out, P.rms_norm(x, w.double(), 1e-5), dtype)
+    # selected rows, no pending add, stream untouched
+    rows = torch.tensor([8, 2], dtype=torch.int32, device=cuda_device)
+    keep = resid.clone()
+    out2 = torch.empty(2, H, device=cuda_device, dtype=dtype)
+    ops.add_rmsnorm(resid, None, w, out2, 1e-6, rows=rows, write_back=False)
+    assert torch.equal(resid, keep)
+    _close(out2, P.rms_norm(keep.double()[[8, 2]], w.double(), 1e-6), dtype)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_silu_mul_and_residual_add(cuda_device, dtype):
+    from binfer_b200.csrc import ops
+    gu = (3 * torch.randn(7, 2 * 150, device=cuda_device)).to(dtype)
+    out = torch.empty(7, 150, device=cuda_device, dtype=dtype)
+    ops.silu_mul(gu, out)
+    g, u = gu.double()[:, :150], gu.double()[:, 150:]
+    _close(out, g / (1 + torch.exp(-g)) * u, dtype)
+    resid = torch.randn(7, 150, device=cuda_device)
+    want = resid.double() + out.double()
+    ops.residual_add(resid, out)
+    _close(resid, want, F32)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 63, 65, 130])
+def test_sgemm_true_float32(cuda_device, M):
+    from binfer_b200.csrc import ops
+    N, K = 300, 203
+    a = torch.randn(130, K, device=cuda_device)
+    w = torch.randn(N, K, device=cuda_device)
+    out = torch.empty(M, N, device=cuda_device)
+    ops.sgemm_nt(a[:M], w, out)
+    ref = a[:M].double() @ w.double().T
+    assert float((out.double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max()) * math.sqrt(K)
+    # a row's result does not depend on how many rows share the call (one order of summation)
+    big = torch.empty(130, N, device=cuda_device)
+    ops.sgemm_nt(a, w, big)
+    assert torch.equal(out, big[:M])
+
+
+# ------------------------------------------------------- q/k norm, rotation, cache write
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nh,nkv,d,rot,norm", [(3, 1, 16, 16, True), (4, 2, 48, 24, True),
+                                               (2, 2, 128, 128, False), (5, 5, 80, 0, True)])
+def test_qk_norm_rope_kv_write(cuda_device, dtype, nh, nkv, d, rot, norm):
+    from binfer_b200.csrc import ops
+    T, ps, pages, eps, theta = 11, 4, 9, 1e-5, 5000.0
+    dev = cuda_device
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device=dev).to(dtype)
+    qw = (1 + 0.1 * torch.randn(d, device=dev)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, device=dev)) if norm else None
+    pos = torch.tensor([0, 1, 2, 3, 40, 41, 1000, 7, 8, 9, 10], dtype=torch.int32, device=dev)
+    slots = torch.randperm(pages * ps)[:T].to(torch.int32).to(dev)
+    slots[3] = -1                                   # this token is not written
+    inv = None
+    if rot:
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        inv = (theta ** (-2.0 * i / rot)).float().to(dev)
+    kc = torch.zeros(pages, nkv, ps, d, device=dev, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, nh * d, device=dev, dtype=dtype)
+    err = _err(dev)
+    ops.qk_norm_rope_kv_write(qkv, qw, kw, inv, pos, slots, q_out, kc, vc, nh, nkv, d, eps, err)
+    assert int(err.item()) == 0
+    x = qkv.double().cpu()
+    q = x[:, :nh * d].view(T, nh, d)
+    k = x[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+    v = x[:, (nh + nkv) * d:].view(T, nkv, d)
+    if norm:
+        q, k = P.rms_norm(q, qw.double().cpu(), eps), P.rms_norm(k, kw.double().cpu(), eps)
+    if rot:
+        ang = P.rope_angles(pos.cpu(), rot, theta)
+        q, k = P.apply_rope(q, ang), P.apply_rope(k, ang)
+    _close(q_out.view(T, nh, d), q, dtype)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        _close(kc[s // ps, :, s % ps], k[t], dtype)
+        _close(vc[s // ps, :, s % ps], v[t], dtype)
+    assert float(kc.abs().sum(dim=(1, 3)).flatten().count_nonzero()) == T - 1
+
+
+# ----------------------------------------------------------------------- attention
+def _paged(k, v, ps, dev, dtype, seed=0):
+    """Scatter dense k, v ``[n, nkv, d]`` of one request into shuffled pages.
+    Returns caches ``[pages, nkv, ps, d]`` and the block table."""
+    n, nkv, d = k.shape
+    n_pages = -(-n // ps)
+    total = n_pages + 5
+    g = torch.Generator().manual_seed(seed)
+    ids = (torch.randperm(total - 1, generator=g)[:n_pages] + 1).tolist()   # page 0 unused
+    kc = torch.randn(total, nkv, ps, d, generator=g).to(dtype)              # junk elsewhere
+    vc = torch.randn(total, nkv, ps, d, generator=g).to(dtype)
+    for j in range(n):
+        kc[ids[j // ps], :, j % ps] = k[j].to(dtype)
+        vc[ids[j // ps], :, j % ps] = v[j].to(dtype)
+    return kc.to(dev), vc.to(dev), ids
+
+
+def _attention_case(dev, dtype, nh, nkv, d, ps, ctxs, qlens, window, spike=False, seed=0):
+    """Requests with contexts ``ctxs``, the last ``qlens`` tokens of each being queries."""
+    g = torch.Generator().manual_seed(seed)
+    ks, vs, qs, tables, refs = [], [], [], [], []
+    kcs, vcs = [], []
+    page_base = 0
+    for b, (n, ql) in enumerate(zip(ctxs, qlens)):
+        k = torch.randn(n, nkv, d, generator=g).to(dtype).double()
+        v = torch.randn(n, nkv, d, generator=g).to(dtype).double()
+        q = torch.randn(n, nh, d, generator=g).to(dtype).double()
+        if spike and n > 40:
+            # one far key stands out: its score beats hundreds of others.  With a window it
+            # is the first key inside the last query's window, and the key just outside
+            # stands out even more, so reading one key too many shows as well.
+            far = 3 if window is None else max(0, n - window)
+            k[far] = 0
+            k[far, :, 0] = 32.0
+            q[-1, :, 0] = 16.0
+            v[far] = 5.0
+            if window is not None and far > 0:
+                k[far - 1] = 0
+                k[far - 1, :, 0] = 64.0
+                v[far - 1] = -7.0
+        ref = P.causal_attention(q, k, v, d ** -0.5, window)[n - ql:]
+        kc, vc, ids = _paged(k, v, ps, "cpu", dtype, seed + b)
+        kcs.append(kc)
+        vcs.append(vc)
+        tables.append([i + page_base for i in ids])
+        page_base += kc.shape[0]
+        qs.append(q[n - ql:])
+        refs.append(ref)
+    width = max(len(t) for t in tables)
+    bt = torch.zeros(len(ctxs), width, dtype=torch.int32)
+    for b, t in enumerate(tables):
+        bt[b, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_all = torch.cat(qs).to(dtype).reshape(-1, nh * d).to(dev)
+    pos = torch.cat([torch.arange(n - ql, n) for n, ql in zip(ctxs, qlens)]).to(torch.int32).to(dev)
+    sot = torch.cat([torch.full((ql,), b) for b, ql in enumerate(qlens)]).to(torch.int32).to(dev)
+    return (q_all, torch.cat(kcs).to(dev), torch.cat(vcs).to(dev), sot, pos, bt.to(dev),
+            torch.cat(refs).reshape(-1, nh * d))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nh,nkv,d,ps,window,spike", [
+    (4, 2, 16, 16, None, False), (6, 1, 32, 8, None, True), (5, 5, 48, 4, 24, True),
+    (8, 2, 128, 16, None, True), (3, 3, 80, 5, 33, False), (2, 1, 256, 16, 100, True)])
+def test_paged_attention_generic(cuda_device, dtype, nh, nkv, d, ps, window, spike):
+    from binfer_b200.csrc import ops
+    ctxs, qlens = [70, 1, 129, 300], [70, 1, 5, 2]
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, dtype, nh, nkv, d, ps, ctxs,
+                                                   qlens, window, spike)
+    out = torch.empty_like(q)
+    err = _err(cuda_device)
+    ops.paged_attention_generic(q, kc, vc, sot, pos, bt, out, nh, nkv, d, window, d ** -0.5, err)
+    assert int(err.item()) == 0
+    _close(out, ref, dtype)
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window,spike", [
+    (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
+    (32, 8, 128, 16, None, False), (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 200, True),
+    (2, 1, 256, 16, 100, True), (20, 1, 64, 16, None, True), (4, 4, 128, 64, 130, True)])
+def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike):
+    """Contexts on both sides of the 128-key split edge, and long ones."""
+    from binfer_b200.csrc import ops
+    ctxs = [1, 127, 128, 129, 300, 1000, 45]
+    qlens = [1] * len(ctxs)
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   qlens, window, spike, seed=3)
+    out = torch.zeros_like(q)
+    err = _err(cuda_device)
+    ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, window,
+                         d ** -0.5, max(ctxs) + 500, err)
+    assert int(err.item()) == 0
+    _close(out, ref, BF16)
+    # a subset of rows, given by index, gives the same bits for those rows
+    rows = torch.tensor([5, 2, 4], dtype=torch.int32, device=cuda_device)
+    out2 = torch.zeros_like(q)
+    ops.decode_attention(q, kc, vc, rows, 3, sot, pos, bt, out2, nh, nkv, d, window,
+                         d ** -0.5, max(ctxs), err)
+    for r in (5, 2, 4):
+        assert torch.equal(out2[r], out[r])
+    assert float(out2[0].abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------------ sampling
+def _sample(dev, logits, temperature, top_k=0, top_p=1.0, u=0.0):
+    from binfer_b200.csrc import ops
+    R = logits.shape[0]
+    f = lambda v, dt: torch.full((R,), v, dtype=dt, device=dev)
+    uu = torch.as_tensor(u, dtype=torch.float32, device=dev).expand(R).contiguous()
+    out = torch.empty(R, dtype=torch.int32, device=dev)
+    ops.sample(logits, f(temperature, torch.float32), f(top_k, torch.int32),
+               f(top_p, torch.float32), uu, out)
+    return out.cpu().tolist()
+
+
+def test_argmax_lowest_index_on_ties(cuda_device):
+    logits = torch.randn(5, 3001, device=cuda_device)
+    logits[0, [7, 2000, 2999]] = 50.0
+    logits[1, 3000] = 50.0
+    logits[2, 0] = 50.0
+    logits[3] = 1.0                                   # all equal
+    got = _sample(cuda_device, logits, 0.0)
+    assert got[:4] == [7, 3000, 0, 0]
+    assert got[4] == int(torch.argmax(logits[4]))
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.6),
+                                                     (1.0, 40, 0.9), (2.0, 1, 1.0)])
+def test_sampling_matches_plain_sampler(cuda_device, temperature, top_k, top_p):
+    g = torch.Generator().manual_seed(5)
+    V = 1237
+    logits = (3 * torch.randn(24, V, generator=g))
+    us = torch.rand(24, generator=g)
+    got = _sample(cuda_device, logits.to(cuda_device), temperature, top_k, top_p, us)
+    for r in range(24):
+        want = P.sample(logits[r], temperature, top_k, top_p, uniform=float(us[r]))
+        if got[r] != want:
+            # only a draw that lands within float rounding of a boundary may differ
+            s = logits[r].double() / temperature
+            p = torch.softmax(s, 0)
+            cum = torch.cumsum(p, 0)
+            assert abs(float(cum[min(got[r], want)]) - float(us[r])) < 1e-4, (r, got[r], want)
+
+
+def test_top_k_confines_support_and_penalty(cuda_device):
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(1)
+    logits = torch.randn(1, 500, generator=g)
+    top = set(torch.topk(logits[0], 5).indices.tolist())
+    dev_logits = logits.to(cuda_device).repeat(64, 1).contiguous()
+    got = _sample(cuda_device, dev_logits, 1.5, top_k=5, u=torch.rand(64, generator=g))
+    assert set(got) <= top and len(set(got)) > 1
+    # repetition penalty flips the argmax (s > 0 ? s / pen : s * pen), twice for two occurrences
+    lg = torch.tensor([[1.0, 3.0, 2.9, -1.0]], device=cuda_device)
+    items = torch.tensor([[0, 1, 2], [0, 3, 1]], dtype=torch.int32, device=cuda_device)
+    ops.repetition_penalty(lg, items, torch.tensor([1.5], device=cuda_device))
+    assert torch.allclose(lg.cpu(), torch.tensor([[1.0, 3.0 / 2.25, 2.9, -1.5]]))
+    assert _sample(cuda_device, lg, 0.0) == [2]
