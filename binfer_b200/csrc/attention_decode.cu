@@ -348,3 +348,63 @@ BF_EXPORT int bf_decode_attention(const void* q, const void* k_cache, const void
 }
 
 BF_EXPORT int bf_decode_attention_split_keys() { return DEC_SPLIT; }
+
+// ------------------------------------------------------------------------------
+// The same attention with its scratch inside the library (see the header for who
+// needs this and for the rules of use).  Host code must not pass the array's
+// name to a kernel: on the host that name is only a handle for the runtime.  Its
+// device address is looked up once per device and kept.
+#include "attention_decode_static.h"
+
+static __device__ __align__(256) unsigned char bf_decode_static_scratch[BF_DECODE_STATIC_SCRATCH_BYTES];
+
+#define BF_STATIC_MAX_DEVICES 64
+static void* bf_decode_static_ptr[BF_STATIC_MAX_DEVICES];   // device address, per device
+
+BF_EXPORT const char* bf_decode_attention_static_error(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case BF_STATIC_ERR_TOO_LARGE:
+      return "n_rows * nh * max_splits * (d + 2) * 4 bytes exceeds the library's 8 MiB scratch "
+             "array; use fewer rows or splits per call, or bf_decode_attention with scratch of "
+             "your own";
+    case BF_STATIC_ERR_HEAD_DIM: return "head size must be one of 32, 64, 96, 128, 256";
+    case BF_STATIC_ERR_ARGUMENT: return "a required pointer is null or a size is not positive";
+    case BF_STATIC_ERR_DEVICE: return "the current device index is beyond the 64 the library tracks";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
+  }
+}
+
+BF_EXPORT int bf_decode_attention_static(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* rows, const int* seq_of_token,
+                                         const int* positions, const int* block_tables,
+                                         int table_stride, void* out, int n_rows, int nh, int nkv,
+                                         int d, int page_size, int num_pages, int window,
+                                         int max_splits, float scale, int* err,
+                                         cudaStream_t stream) {
+  if (!q || !k_cache || !v_cache || !seq_of_token || !positions || !block_tables || !out || !err)
+    return BF_STATIC_ERR_ARGUMENT;
+  if (n_rows <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_splits <= 0)
+    return BF_STATIC_ERR_ARGUMENT;
+  if (d != 32 && d != 64 && d != 96 && d != 128 && d != 256) return BF_STATIC_ERR_HEAD_DIM;
+  const unsigned long long cells = (unsigned long long)n_rows * nh * max_splits;
+  const unsigned long long need = cells * (unsigned long long)(d + 2) * sizeof(float);
+  if (need > BF_DECODE_STATIC_SCRATCH_BYTES) return BF_STATIC_ERR_TOO_LARGE;
+
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= BF_STATIC_MAX_DEVICES) return BF_STATIC_ERR_DEVICE;
+  if (!bf_decode_static_ptr[dev]) {
+    // once per device, with that device current: the array's address on this device
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, bf_decode_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    bf_decode_static_ptr[dev] = p;
+  }
+  float* part_o = reinterpret_cast<float*>(bf_decode_static_ptr[dev]);
+  float* part_ml = part_o + cells * d;      // behind the outputs' partials; 8-byte aligned
+  return bf_decode_attention(q, k_cache, v_cache, rows, seq_of_token, positions, block_tables,
+                             table_stride, out, part_o, part_ml, n_rows, nh, nkv, d, page_size,
+                             num_pages, window, max_splits, scale, err, stream);
+}
