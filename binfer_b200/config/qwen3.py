@@ -168,7 +168,9 @@ class Qwen3Config:
             bad = sorted(set(self.layer_types) - {"full_attention", "sliding_attention"})
             if bad:
                 raise ConfigError(f"unknown layer_types entries: {bad}")
-        if any(w for w in self.layer_windows()) and not self.sliding_window:
+        sliding = self.use_sliding_window or (
+            self.layer_types is not None and "sliding_attention" in self.layer_types)
+        if sliding and not (self.sliding_window and self.sliding_window > 0):
             raise ConfigError("sliding attention layers need a positive sliding_window")
 
     # ------------------------------------------------------------- derivation

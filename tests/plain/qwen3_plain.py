@@ -177,7 +177,7 @@ def sample(logits: torch.Tensor, temperature: float = 0.0, top_k: int = 0, top_p
     returns the first whose running sum exceeds ``uniform``."""
     s = logits.to(torch.float64).clone()
     if repetition_penalty != 1.0:
-        for t in set(generated):
+        for t in generated:                 # once per occurrence (sampler.ts:64-73)
             s[t] = s[t] / repetition_penalty if s[t] > 0 else s[t] * repetition_penalty
     if temperature == 0:
         return int(torch.argmax(s))          # torch returns the first maximal index

@@ -1,0 +1,145 @@
+"""The cache manager on the host: no page lost, held twice or freed twice (no GPU)."""
+import random
+
+import pytest
+
+from binfer_b200.cache import CacheManager, KVNeed, OutOfPages, PagePool, SlotPool, StateNeed
+
+
+def _mgr(pages=8, page_size=4, window=None, max_requests=4):
+    needs = [KVNeed(2, 16), KVNeed(2, 16, window) if window else KVNeed(2, 16), None]
+    return CacheManager(needs, [None, None, StateNeed((3,))], page_size=page_size,
+                        num_pages=pages, max_requests=max_requests)
+
+
+def test_page_pool_reuses_last_freed_first_and_never_hands_out_page_zero():
+    pool = PagePool(3)
+    a, b, c = pool.alloc(), pool.alloc(), pool.alloc()
+    assert sorted([a, b, c]) == [1, 2, 3]
+    with pytest.raises(OutOfPages):
+        pool.alloc()
+    pool.free(b)
+    assert pool.alloc() == b
+    pool.free(a)
+    with pytest.raises(ValueError, match="freed twice"):
+        pool.free(a)
+    with pytest.raises(ValueError):
+        pool.free(0)
+    with pytest.raises(ValueError):
+        pool.free(4)
+
+
+def test_slot_pool():
+    s = SlotPool(2)
+    a, b = s.alloc(), s.alloc()
+    with pytest.raises(OutOfPages):
+        s.alloc()
+    s.free(a)
+    with pytest.raises(ValueError):
+        s.free(a)
+    assert s.alloc() == a
+
+
+def test_groups_by_geometry_and_window():
+    m = _mgr(window=8)
+    assert len(m.groups) == 2
+    assert m.entry_location == [(0, 0), (1, 0), None]
+    same = _mgr()
+    assert len(same.groups) == 1 and same.entry_location == [(0, 0), (0, 1), None]
+
+
+def test_reserve_is_all_or_nothing():
+    m = _mgr(pages=4, page_size=4)
+    m.add_request("a")
+    m.reserve("a", 9)                       # 3 pages
+    m.commit("a", 9)
+    m.add_request("b")
+    before = (m.num_free_pages(), [list(t) for t in m.get("b").tables])
+    assert not m.can_reserve([("b", 8)])
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 8)                   # needs 2, only 1 free
+    assert (m.num_free_pages(), [list(t) for t in m.get("b").tables]) == before
+    m.reserve("b", 4)
+    m.check_consistent()
+    assert m.num_free_pages() == [0]
+    assert m.can_reserve([("a", 12)]) and not m.can_reserve([("a", 13)])
+
+
+def test_free_gives_everything_back_and_rejects_unknown():
+    m = _mgr()
+    m.add_request(1)
+    m.reserve(1, 20)
+    m.commit(1, 20)
+    slot = m.get(1).slot
+    m.free_request(1)
+    assert m.num_free_pages() == [8] and m.slots.num_free == 4
+    with pytest.raises(KeyError):
+        m.free_request(1)
+    m.add_request(2)
+    assert m.get(2).slot == slot and m.get(2).fresh
+    with pytest.raises(ValueError, match="already live"):
+        m.add_request(2)
+
+
+def test_window_pages_are_given_back_as_the_window_passes():
+    m = _mgr(pages=6, page_size=4, window=8)
+    m.add_request("r")
+    full, win = m.groups
+    for new_len in range(1, 41):            # token by token
+        if new_len > 24:
+            # the full-attention group is exhausted at 24 tokens; the windowed one goes on
+            with pytest.raises(OutOfPages):
+                m.reserve("r", new_len)
+            break
+        m.reserve("r", new_len)
+        m.commit("r", new_len)
+        m.check_consistent()
+        held = [p for p in m.get("r").tables[1] if p > 0]
+        assert len(held) <= 3               # window 8 over pages of 4: at most 3 pages live
+    t = m.get("r").tables[1]
+    # query at position 24 reads keys 17..24: pages 0..3 are passed
+    m.release_passed("r")
+    assert t[:4] == [-1, -1, -1, -1] and all(p > 0 for p in t[4:])
+    m.free_request("r")
+    assert m.num_free_pages() == [6, 6]
+
+
+def test_window_first_needed_page():
+    m = _mgr(page_size=4, window=8)
+    g = m.groups[1]
+    assert [g.first_needed_page(n) for n in (0, 7, 8, 11, 12)] == [0, 0, 0, 1, 1]
+    assert m.groups[0].first_needed_page(1000) == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_lose_no_page(seed):
+    rng = random.Random(seed)
+    window = rng.choice([None, 6, 13])
+    m = _mgr(pages=rng.randint(6, 20), page_size=rng.choice([1, 3, 4, 16]), window=window,
+             max_requests=5)
+    live = {}
+    for step in range(400):
+        op = rng.random()
+        if op < 0.25 and len(live) < 5:
+            rid = f"q{step}"
+            m.add_request(rid)
+            live[rid] = 0
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            new_len = live[rid] + rng.randint(1, 9)
+            try:
+                m.reserve(rid, new_len)
+            except OutOfPages:
+                assert not m.can_reserve([(rid, new_len)])
+            else:
+                m.commit(rid, new_len)
+                live[rid] = new_len
+        elif live:
+            rid = rng.choice(list(live))
+            m.free_request(rid)
+            del live[rid]
+        m.check_consistent()
+    for rid in list(live):
+        m.free_request(rid)
+    assert m.num_free_pages() == [g.pool.num_pages for g in m.groups]
+    assert m.slots.num_free == 5
