@@ -166,6 +166,9 @@ def main():
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (named in the record)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="only the device-timed decode steps (for profiling): no e2e, no points")
+    ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -186,12 +189,14 @@ def main():
         raw["num_hidden_layers"] = args.layers
     cfg = Qwen3Config.from_dict(raw)
     steps, warmup, B = args.steps, args.warmup, args.batch
+    if args.decode_only:
+        args.no_points = True
     max_b = max(B, 1 if args.no_points else 64)
     pages = max_b * (CONTEXT // PAGE_SIZE) + 64
     t0 = time.time()
     engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=pages, page_size=PAGE_SIZE,
                     max_seq_len=CONTEXT, max_batch_size=max_b, max_tokens_per_step=2048,
-                    cuda_graphs=True)
+                    cuda_graphs=not args.eager)
     runner, sampler = engine.runner, engine.sampler
     vocab = cfg.vocab_size
     gen = torch.Generator().manual_seed(0)
@@ -219,6 +224,13 @@ def main():
     bytes_step = weight_bytes + B * mean_ctx * kv_per_token
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     clk = clocks.summary(*span)
+
+    if args.decode_only:
+        clocks.stop()
+        print(json.dumps({"decode_only": True, "ms_per_step": ms_step, "value": value,
+                          "layers": cfg.num_hidden_layers, "batch": B,
+                          "roofline_frac": achieved / peaks["hbm_gbs"], "clocks": clk}))
+        return 0
 
     # ---- end to end through the entry point: scheduler, H2D inputs, D2H ids every step
     prompts = [torch.randint(0, vocab, (CONTEXT - (steps + warmup) - 1,), generator=gen).tolist()
@@ -288,7 +300,7 @@ def main():
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
             "vocab": cfg.vocab_size, "tied": cfg.tie_word_embeddings, "global_batch": B,
             "seq_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "1 GPU",
-            "cuda_graphs": True, "l2": "inputs larger than L2 (weights 15 GB per step)",
+            "cuda_graphs": not args.eager, "l2": "inputs larger than L2 (weights 15 GB per step)",
             "peaks": peaks["source"],
         },
         "clocks": clk,

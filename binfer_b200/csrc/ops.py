@@ -230,6 +230,43 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                              _stream())
 
 
+_num_sms = {}
+_err_words = {}
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    """The device's int32 error word, which kernels OR bits into instead of faulting."""
+    w = _err_words.get(device.index)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _err_words[device.index] = w
+    return w
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
+              bn: int = 0) -> bool:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float
+    accumulate, bfloat16 or float32 out).  ``bn``: feature rows per tile (0: chosen by the
+    library).  Returns False, having done nothing, for shapes the kernel does not take
+    (K not a multiple of 8, misaligned rows)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_bf16: operands must be bfloat16")
+    M, K = x.shape
+    N = w.shape[0]
+    if (K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8
+            or x.data_ptr() % 16 or w.data_ptr() % 16 or out.stride(1) != 1):
+        return False
+    sms = _num_sms.get(x.device.index)
+    if sms is None:
+        sms = torch.cuda.get_device_properties(x.device).multi_processor_count
+        _num_sms[x.device.index] = sms
+    _run("gemm_bf16_tcgen05", lib().bf_gemm_bf16_tcgen05, _ptr(x), _ptr(w), _ptr(out),
+         _c_int(M), _c_int(N), _c_int(K), _c_ll(x.stride(0)), _c_ll(w.stride(0)),
+         _c_ll(out.stride(0)), _c_int(_dtype_code(out)), _c_int(bn), _c_int(sms), _ptr(err),
+         _stream())
+    return True
+
+
 # -------------------------------------------------------------------- sampling
 def repetition_penalty(logits: torch.Tensor, items: torch.Tensor, penalty: torch.Tensor) -> None:
     """items: int32 [n, 3] of (row, token, count)."""

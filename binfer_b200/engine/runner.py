@@ -74,7 +74,8 @@ class ModelRunner:
         if any(g.storage is None for g in cache.groups):
             cache.allocate_storage(env.dtype, env.device)
         self.views = model.entry_views(cache)
-        self.err = torch.zeros(1, dtype=torch.int32, device=env.device)
+        from ..csrc import ops
+        self.err = ops.error_word(env.device)
         self._staging = _Staging()
         self.steps = 0
         self.h2d_bytes = 0

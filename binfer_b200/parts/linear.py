@@ -1,17 +1,41 @@
 """The dense matrix product ``y = x W^T`` with weights as stored (``[out, in]`` row-major).
 
 float32 engine: the engine's own FP32-FMA kernel (no reduced-precision matrix mode).
-bfloat16 engine: cuBLAS through ``torch.mm`` with float accumulation, the same
-library call the reference makes for every dense product
-(cuda/kernels/gemm.cu:244-267: ``cublasGemmEx``, bf16 in, ``CUBLAS_COMPUTE_32F``).
+bfloat16 engine: the engine's tcgen05/TMEM/TMA kernel (``csrc/gemm_tcgen05.cu``) or
+cuBLAS through ``torch.mm`` with float accumulation, the library call the reference
+makes for every dense product (cuda/kernels/gemm.cu:244-267: ``cublasGemmEx``, bf16
+in, ``CUBLAS_COMPUTE_32F``).  Which one: ``BINFER_B200_GEMM=own`` takes the engine's
+kernel for every shape it accepts, ``library`` never, and ``auto`` (the default)
+where it was measured to be at least as fast as the library on a B200: few tokens
+against a wide weight (the gate/up projection and the output head while decoding).
 """
 from __future__ import annotations
 
 from typing import Optional
 
+import os
+
 import torch
 
 from ..csrc import ops
+
+_POLICY = os.environ.get("BINFER_B200_GEMM", "auto")
+
+
+def set_gemm_policy(policy: str) -> None:
+    """``own``, ``library`` or ``auto`` (see the module text)."""
+    global _POLICY
+    if policy not in ("own", "library", "auto"):
+        raise ValueError(f"unknown GEMM policy {policy!r}")
+    _POLICY = policy
+
+
+def _use_own(M: int, N: int, K: int) -> bool:
+    if _POLICY == "own":
+        return True
+    if _POLICY == "library":
+        return False
+    return M <= 128 and N >= 16384
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -26,6 +50,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         return out
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
+    if _use_own(M, N, x.shape[1]):
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+        if ops.gemm_bf16(x, w, out, ops.error_word(x.device)):
+            return out
     prof = ops._profiler
     if prof is not None:
         prof.begin("cublas_gemm_bf16")

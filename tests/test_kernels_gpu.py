@@ -291,3 +291,67 @@ def test_top_k_confines_support_and_penalty(cuda_device):
     ops.repetition_penalty(lg, items, torch.tensor([1.5], device=cuda_device))
     assert torch.allclose(lg.cpu(), torch.tensor([[1.0, 3.0 / 2.25, 2.9, -1.5]]))
     assert _sample(cuda_device, lg, 0.0) == [2]
+
+
+# ------------------------------------------------------------- tcgen05 matrix product
+@pytest.mark.parametrize("M,N,K", [(1, 300, 200), (8, 128, 64), (7, 6144, 4096), (16, 4096, 4104),
+                                   (33, 1000, 512), (64, 4096, 12288), (65, 272, 72),
+                                   (128, 256, 64), (200, 700, 1000), (513, 2100, 2048)])
+@pytest.mark.parametrize("out_dtype", [BF16, F32])
+def test_gemm_bf16_tcgen05(cuda_device, M, N, K, out_dtype):
+    """Token counts on both sides of the 128-row tile, widths and depths that are no
+    multiple of the tile, bfloat16 and float32 results."""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(BF16).to(cuda_device)
+    out = torch.full((M, N), 99.0, device=cuda_device, dtype=out_dtype)
+    err = ops.error_word(cuda_device)
+    assert ops.gemm_bf16(x, w, out, err)
+    assert int(err.item()) == 0
+    ref = x.double().cpu() @ w.double().cpu().T
+    if out_dtype == BF16:
+        _close(out, ref, BF16)
+    else:
+        # float accumulation of K products in the tensor core: error grows like sqrt(K)
+        err_rel = float((out.double().cpu() - ref).abs().max() / ref.abs().max())
+        assert err_rel <= 4e-7 * math.sqrt(K), err_rel
+    # every tile width gives the same sums (one order of accumulation over K)
+    for bn in (16, 48, 256):
+        other = torch.empty_like(out)
+        assert ops.gemm_bf16(x, w, other, err, bn=bn)
+        assert torch.equal(other, out), f"tile width {bn} changes the result"
+
+
+def test_gemm_bf16_refuses_what_it_cannot_take(cuda_device):
+    from binfer_b200.csrc import ops
+    x = torch.randn(4, 100, device=cuda_device).to(BF16)       # K not a multiple of 8
+    w = torch.randn(32, 100, device=cuda_device).to(BF16)
+    out = torch.full((4, 32), 5.0, device=cuda_device, dtype=BF16)
+    assert not ops.gemm_bf16(x, w, out, ops.error_word(cuda_device))
+    assert bool((out == 5.0).all())
+
+
+def test_engine_with_own_gemm_everywhere(cuda_device, tmp_path):
+    """The bfloat16 engine with every product on the tcgen05 kernel still matches the plain
+    implementation (config with hidden sizes that are multiples of 8)."""
+    import helpers as H
+    from binfer_b200.engine import make_env, make_runner, model_from_dir
+    import importlib
+    L = importlib.import_module("binfer_b200.parts.linear")
+    d = H.make_model_dir(tmp_path, "B", BF16)
+    raw, w = H.read_model_dir(d)
+    reqs = {f"r{i}": H.random_tokens(n, raw["vocab_size"], n) for i, n in enumerate([70, 150, 9])}
+    ref = {rid: P.forward(raw, w, t, torch.float64) for rid, t in reqs.items()}
+    before = L._POLICY
+    L.set_gemm_policy("own")
+    try:
+        env = make_env(BF16)
+        steps = H.trace_mixed(reqs)
+        runner = make_runner(model_from_dir(d, env), env, page_size=8,
+                             num_pages=H.peak_pages(steps, 8))
+        got = H.run_trace(runner, steps)
+    finally:
+        L.set_gemm_policy(before)
+    worst = max(H.rel_err(row, ref[rid][p]) for (rid, p), row in got.items())
+    assert worst <= 3e-2, worst
