@@ -214,6 +214,22 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _launches += 1          # two kernels: the splits and their merge
 
 
+def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      items: torch.Tensor, n_items: int, max_rows: int,
+                      block_tables: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, d: int,
+                      window: Optional[int], scale: float, err: torch.Tensor) -> None:
+    """Causal flash attention over the pages for prompt portions (bfloat16 only).
+    ``items`` int32 [n, 4]: (request index, first token row, rows, first position)."""
+    if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
+        raise KernelError(f"prefill_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
+    _want(items, torch.int32, "items")
+    _run("prefill_attention", lib().bf_prefill_attention,
+         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items), _c_int(max_rows),
+         _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv),
+         _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]), _c_int(window or 0),
+         _c_float(scale), _ptr(err), _stream())
+
+
 # ------------------------------------------------------------- matrix products
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic."""

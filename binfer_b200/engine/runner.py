@@ -88,12 +88,13 @@ class ModelRunner:
         self.cache.free_request(rid)
 
     # -------------------------------------------------------------- the batch
-    def _layout(self, T: int, B: int, R: int, widths: Sequence[int]):
+    def _layout(self, T: int, B: int, R: int, widths: Sequence[int], n_dec: int = 0,
+                n_pf: int = 0):
         """Offsets (in int32 elements) of each field inside the batch description."""
         off, fields = 0, {}
         for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T),
                         ("q_start", B + 1), ("ctx_lens", B), ("state_slots", B),
-                        ("logit_rows", R)):
+                        ("logit_rows", R), ("decode_rows", n_dec), ("prefill_items", 4 * n_pf)):
             fields[name] = (off, n)
             off += n
         for g, w in enumerate(widths):
@@ -127,7 +128,10 @@ class ModelRunner:
             R = sum(len(it.want) for it in items)
         if widths is None:
             widths = [max(1, max(len(rc.tables[g.index]) for rc in rcs)) for g in cache.groups]
-        fields, total = self._layout(T, B, R, widths)
+        mixed = not pad_to and any(n > 1 for n in q_lens)
+        dec = [b for b, n in enumerate(q_lens) if n == 1] if mixed else []
+        pf = [b for b, n in enumerate(q_lens) if n > 1] if mixed else []
+        fields, total = self._layout(T, B, R, widths, len(dec), len(pf))
         host, ring = self._staging.take(total)
         h = host.numpy()
         h[:total] = 0
@@ -153,6 +157,11 @@ class ModelRunner:
                     rows[r] = t + w
                     r += 1
             t += n
+        if mixed:
+            view("decode_rows")[:] = [int(qs[b]) for b in dec]
+            items4 = view("prefill_items").reshape(len(pf), 4)
+            for i, b in enumerate(pf):
+                items4[i] = (b, int(qs[b]), q_lens[b], starts[b])
         for b in range(n_real, B):              # padding rows
             sot[b] = b
             qs[b] = b
@@ -196,7 +205,11 @@ class ModelRunner:
                           for g in cache.groups],
             logit_rows=dview("logit_rows"), err=self.err,
             q_lens=q_lens, ctx_lens_host=ctx_lens, max_q_len=max(q_lens),
-            max_ctx_len=max(ctx_lens), decode_only=all(n == 1 for n in q_lens))
+            max_ctx_len=max(ctx_lens), decode_only=all(n == 1 for n in q_lens),
+            decode_rows=dview("decode_rows") if dec else None, n_decode=len(dec),
+            max_decode_ctx=max([ctx_lens[b] for b in dec], default=1),
+            prefill_items=dview("prefill_items").view(len(pf), 4) if pf else None,
+            n_prefill=len(pf), max_prefill_rows=max([q_lens[b] for b in pf], default=0))
 
     # ---------------------------------------------------------------- the step
     def reserve(self, items: Sequence[StepItem]) -> None:

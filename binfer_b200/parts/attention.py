@@ -100,15 +100,24 @@ class GQAAttention(Mixer):
         s = self.spec
         tables = ctx.block_tables[view.group]
         fast = q.dtype == torch.bfloat16 and s.head_dim in ops.DECODE_HEAD_DIMS
-        if fast and ctx.decode_only:
-            ops.decode_attention(
-                q, view.k_cache, view.v_cache, None, ctx.T, ctx.seq_of_token, ctx.positions,
-                tables, out, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale,
-                ctx.max_ctx_len, ctx.err)
+        if not fast:
+            ops.paged_attention_generic(
+                q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, tables, out,
+                s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale, ctx.err)
             return
-        ops.paged_attention_generic(
-            q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, tables, out,
-            s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale, ctx.err)
+        common = (s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale)
+        if ctx.decode_only:
+            ops.decode_attention(q, view.k_cache, view.v_cache, None, ctx.T, ctx.seq_of_token,
+                                 ctx.positions, tables, out, *common, ctx.max_ctx_len, ctx.err)
+            return
+        if ctx.n_decode:
+            ops.decode_attention(q, view.k_cache, view.v_cache, ctx.decode_rows, ctx.n_decode,
+                                 ctx.seq_of_token, ctx.positions, tables, out, *common,
+                                 ctx.max_decode_ctx, ctx.err)
+        if ctx.n_prefill:
+            ops.prefill_attention(q, view.k_cache, view.v_cache, ctx.prefill_items,
+                                  ctx.n_prefill, ctx.max_prefill_rows, tables, out, *common,
+                                  ctx.err)
 
 
 register_mixer("attention", GQAAttention)

@@ -57,6 +57,15 @@ class StepContext:
     max_q_len: int = 1
     max_ctx_len: int = 1
     decode_only: bool = False
+    # rows that bring one token, and portions that bring more (for kernels that treat
+    # the two apart): decode_rows int32 [n_decode] of token rows; prefill_items int32
+    # [n_prefill, 4] of (request index, first token row, rows, first position)
+    decode_rows: Optional[torch.Tensor] = None
+    n_decode: int = 0
+    max_decode_ctx: int = 1
+    prefill_items: Optional[torch.Tensor] = None
+    n_prefill: int = 0
+    max_prefill_rows: int = 0
     entry: int = 0                     # schedule entry being run
     scratch: Dict[str, object] = field(default_factory=dict)
 

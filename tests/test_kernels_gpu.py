@@ -355,3 +355,32 @@ def test_engine_with_own_gemm_everywhere(cuda_device, tmp_path):
         L.set_gemm_policy(before)
     worst = max(H.rel_err(row, ref[rid][p]) for (rid, p), row in got.items())
     assert worst <= 3e-2, worst
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window,spike", [
+    (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
+    (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 70, True), (2, 1, 256, 16, 100, True),
+    (4, 4, 128, 64, 130, True)])
+def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike):
+    """Portions that start in the middle of a prompt, straddle 64-key tiles and pages, next to
+    whole prompts; the far key and the window's edge are made to stand out."""
+    from binfer_b200.csrc import ops
+    ctxs, qlens = [70, 200, 129, 300, 64, 2], [70, 37, 5, 130, 64, 2]
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   qlens, window, spike, seed=11)
+    items, row = [], 0
+    for b, (n, ql) in enumerate(zip(ctxs, qlens)):
+        items.append([b, row, ql, n - ql])
+        row += ql
+    items = torch.tensor(items, dtype=torch.int32, device=cuda_device)
+    out = torch.zeros_like(q)
+    err = _err(cuda_device)
+    ops.prefill_attention(q, kc, vc, items, len(ctxs), max(qlens), bt, out, nh, nkv, d, window,
+                          d ** -0.5, err)
+    assert int(err.item()) == 0
+    _close(out, ref, BF16)
+    # a subset of the portions leaves the other rows alone
+    out2 = torch.zeros_like(q)
+    ops.prefill_attention(q, kc, vc, items[1:3].contiguous(), 2, 37, bt, out2, nh, nkv, d,
+                          window, d ** -0.5, err)
+    assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
