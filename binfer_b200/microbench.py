@@ -1,0 +1,175 @@
+"""Time one of the engine's kernels alone, at a given size, against its roofline.
+
+    python -m binfer_b200.microbench decode_attention --batch 8 --ctx 4096
+    python -m binfer_b200.microbench prefill_attention --tokens 2048
+    python -m binfer_b200.microbench gemm --tokens 8 --features 6144 --k 4096 [--library]
+    python -m binfer_b200.microbench add_rmsnorm --tokens 8 --hidden 4096
+
+Sizes default to the Qwen3-8B shape.  Each kernel runs on a rotation of input sets
+larger than the L2 cache, after warm-up, between CUDA events; the line printed gives
+microseconds per launch, the bytes or flops the kernel has to move, and the
+fraction of the measured peak (``MEASURED_PEAKS.json`` beside the package, else the
+stated fallback).  The reference measures its own peaks the same way at run time
+(src/profiler/profiler.ts:553-659).  ``--iters 1 --warmup 0`` gives a run small
+enough to put under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from .csrc import ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BF16 = torch.bfloat16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timed(fns, iters, warmup):
+    """Microseconds per call of fns[i % len(fns)]() (a rotation of input sets)."""
+    for i in range(warmup):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fns[i % len(fns)]()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
+def report(name, us, nbytes=None, flops=None, **extra):
+    hbm, tf, src = peaks()
+    out = {"kernel": name, "us": round(us, 2), **extra}
+    if nbytes is not None:
+        out["GB/s"] = round(nbytes / us / 1e3, 1)
+        out["frac_of_hbm_peak"] = round(nbytes / us / 1e3 / hbm, 3)
+    if flops is not None:
+        out["TFLOP/s"] = round(flops / us / 1e6, 1)
+        out["frac_of_bf16_peak"] = round(flops / us / 1e6 / tf, 3)
+    out["peaks"] = src
+    print(json.dumps(out), flush=True)
+
+
+def _paged_cache(dev, n_req, ctx, nkv, d, ps, sets):
+    """Random caches for n_req requests of ctx tokens, pages handed out in shuffled order."""
+    pages_per = -(-ctx // ps)
+    total = n_req * pages_per + 1
+    out = []
+    for s in range(sets):
+        kc = torch.randn(total, nkv, ps, d, device=dev, dtype=BF16)
+        vc = torch.randn(total, nkv, ps, d, device=dev, dtype=BF16)
+        perm = (torch.randperm(total - 1, device=dev) + 1).to(torch.int32)
+        bt = perm[: n_req * pages_per].view(n_req, pages_per).contiguous()
+        out.append((kc, vc, bt))
+    return out
+
+
+def decode_attention(a):
+    dev = torch.device("cuda:0")
+    B, ctx, nh, nkv, d, ps = a.batch, a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size
+    per_set = 2 * B * ctx * nkv * d * 2
+    sets = max(2, int(3e8 // per_set) + 1)
+    caches = _paged_cache(dev, B, ctx, nkv, d, ps, sets)
+    q = torch.randn(B, nh * d, device=dev, dtype=BF16)
+    out = torch.empty_like(q)
+    sot = torch.arange(B, dtype=torch.int32, device=dev)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+    err = ops.error_word(dev)
+    fns = [lambda c=c: ops.decode_attention(q, c[0], c[1], None, B, sot, pos, c[2], out, nh, nkv, d,
+                                            None, d ** -0.5, ctx, err) for c in caches]
+    us = timed(fns, a.iters, a.warmup)
+    report("decode_attention", us, nbytes=per_set, batch=B, ctx=ctx, heads=nh, kv_heads=nkv,
+           head_dim=d, page_size=ps)
+
+
+def prefill_attention(a):
+    dev = torch.device("cuda:0")
+    T, start, nh, nkv, d, ps = a.tokens, a.start, a.heads, a.kv_heads, a.head_dim, a.page_size
+    ctx = start + T
+    (kc, vc, bt), = _paged_cache(dev, 1, ctx, nkv, d, ps, 1)
+    q = torch.randn(T, nh * d, device=dev, dtype=BF16)
+    out = torch.empty_like(q)
+    items = torch.tensor([[0, 0, T, start]], dtype=torch.int32, device=dev)
+    err = ops.error_word(dev)
+    fn = lambda: ops.prefill_attention(q, kc, vc, items, 1, T, bt, out, nh, nkv, d, None,
+                                       d ** -0.5, err)
+    us = timed([fn], a.iters, a.warmup)
+    flops = 4.0 * nh * d * (T * start + T * (T + 1) / 2)
+    report("prefill_attention", us, flops=flops, tokens=T, start=start, heads=nh, kv_heads=nkv,
+           head_dim=d)
+
+
+def gemm(a):
+    dev = torch.device("cuda:0")
+    M, N, K = a.tokens, a.features, a.k
+    sets = max(2, int(3e8 // (N * K * 2)) + 1)
+    ws = [(0.05 * torch.randn(N, K, device=dev)).to(BF16) for _ in range(sets)]
+    x = torch.randn(M, K, device=dev).to(BF16)
+    out = torch.empty(M, N, device=dev, dtype=BF16)
+    err = ops.error_word(dev)
+    if a.library:
+        fns = [lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]
+    else:
+        fns = [lambda w=w: ops.gemm_bf16(x, w, out, err, bn=a.bn) for w in ws]
+    us = timed(fns, a.iters, a.warmup)
+    report("gemm_library" if a.library else "gemm_bf16_tcgen05", us,
+           nbytes=(N * K + M * K + M * N) * 2, flops=2.0 * M * N * K, tokens=M, features=N, k=K)
+
+
+def add_rmsnorm(a):
+    dev = torch.device("cuda:0")
+    T, H = a.tokens, a.hidden
+    resid = torch.randn(T, H, device=dev)
+    delta = torch.randn(T, H, device=dev).to(BF16)
+    w = torch.ones(H, device=dev)
+    out = torch.empty(T, H, device=dev, dtype=BF16)
+    us = timed([lambda: ops.add_rmsnorm(resid, delta, w, out, 1e-6)], a.iters, a.warmup)
+    report("add_rmsnorm", us, nbytes=T * H * (4 + 4 + 2 + 2), tokens=T, hidden=H)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m binfer_b200.microbench", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=["decode_attention", "prefill_attention", "gemm",
+                                       "add_rmsnorm"])
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--start", type=int, default=0, help="tokens already cached (prefill)")
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--features", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--bn", type=int, default=0, help="feature rows per tile (0: chosen)")
+    ap.add_argument("--library", action="store_true", help="time cuBLAS on the same product")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a CUDA device", file=sys.stderr)
+        return 1
+    ops.lib()
+    {"decode_attention": decode_attention, "prefill_attention": prefill_attention,
+     "gemm": gemm, "add_rmsnorm": add_rmsnorm}[a.kernel](a)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,308 @@
+"""Each part alone against the plain implementation, and parts that the framework does not
+ship, defined here: a mixer with state of its own, a feed-forward with routing, another
+position encoding, a schedule that runs a layer twice and lets a layer read another's pages.
+None of them needs a change to the framework's files."""
+from dataclasses import dataclass
+from typing import Optional
+
+import pytest
+import torch
+
+import helpers as H
+import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def _env(dtype=torch.float32):
+    from binfer_b200.engine import make_env
+    return make_env(dtype)
+
+
+def _ctx_for(runner, items):
+    runner.reserve(items)
+    return runner.build_context(items)
+
+
+def _tiny_runner(which="A", dtype=torch.float32, tmp=None, **kw):
+    from binfer_b200.engine import make_runner, model_from_dir
+    env = _env(dtype)
+    d = H.make_model_dir(tmp, which, dtype)
+    model = model_from_dir(d, env)
+    return model, make_runner(model, env, page_size=H.TINY[which]["page_size"], num_pages=64, **kw), d
+
+
+# ------------------------------------------------------------------ parts alone
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1.2e-2)])
+def test_norm_part_folds_the_pending_add(cuda_device, dtype, tol):
+    from binfer_b200.config import NormSpec
+    from binfer_b200.parts import ResidualStream, build_norm
+    from binfer_b200.weights import ParamSpec
+    env = _env(dtype)
+    norm = build_norm(NormSpec(eps=3e-5), 100, "n.weight", env)
+    assert [(s.name, s.shape, s.role) for s in norm.param_specs()] == [("n.weight", (100,), "vector")]
+    w = 1 + 0.1 * torch.randn(100)
+    norm.load(lambda spec: w.to(env.device))
+    x = torch.randn(6, 100, device=env.device)
+    delta = torch.randn(6, 100, device=env.device).to(dtype)
+    stream = ResidualStream(x.clone())
+    stream.add(delta)
+    y = norm.forward(stream)
+    want_x = x.double() + delta.double()
+    assert stream.pending is None
+    assert H.rel_err(stream.x.cpu(), want_x.cpu()) < 2e-6
+    assert H.rel_err(y.cpu(), P.rms_norm(want_x.cpu(), w.double(), 3e-5)) < tol
+
+
+def test_feed_forward_part(cuda_device, tmp_path):
+    model, runner, d = _tiny_runner("B", tmp=tmp_path)
+    raw, w = H.read_model_dir(d)
+    ffn = model.blocks[1].ffn
+    assert [s.shape for s in ffn.param_specs()] == [(160, 96), (160, 96), (96, 160)]
+    x = torch.randn(13, 96, device=cuda_device)
+    got = ffn.forward(x, None)
+    want = P.swiglu_mlp(x.double().cpu(), {k: v.double() for k, v in w.items()},
+                        "model.layers.1.mlp.")
+    assert H.rel_err(got.cpu(), want) < 5e-6
+
+
+def test_position_encoding_part(cuda_device):
+    from binfer_b200.config import RopeSpec
+    from binfer_b200.parts import build_position
+    rope = build_position(RopeSpec(theta=1e6, rotary_dim=32, factor=4.0), 32, _env())
+    i = torch.arange(16, dtype=torch.float64)
+    assert torch.equal(rope.inv_freq.cpu(), ((1e6 ** (-2 * i / 32)) / 4.0).float())
+    with pytest.raises(ValueError):
+        build_position(RopeSpec(rotary_dim=48), 32, _env())
+
+
+@pytest.mark.parametrize("which", ["A", "B", "W"])
+def test_attention_part_alone(cuda_device, tmp_path, which):
+    """The mixer on normed activations of a whole request, then again as two portions."""
+    from binfer_b200.engine.runner import StepItem
+    model, runner, d = _tiny_runner(which, tmp=tmp_path)
+    raw, w = H.read_model_dir(d)
+    c = P.read_config(raw)
+    layer = 1
+    mixer = model.blocks[layer].mixer
+    view = runner.views[layer]
+    n = 45
+    x = torch.randn(n, c["hidden"], device=cuda_device)
+    want = P.attention_block(x.double().cpu(), {k: v.double() for k, v in w.items()},
+                             f"model.layers.{layer}.self_attn.", c, torch.arange(n),
+                             c["windows"][layer])
+    runner.add_request("r")
+    ctx = _ctx_for(runner, [StepItem("r", list(range(n)), [])])
+    got = mixer.forward(x, ctx, view)
+    assert H.rel_err(got.cpu(), want) < 5e-6
+    runner.free_request("r")
+    runner.add_request("s")                         # the same in two portions, cut at 17
+    ctx = _ctx_for(runner, [StepItem("s", list(range(17)), [])])
+    a = mixer.forward(x[:17], ctx, view)
+    runner.cache.commit("s", 17)
+    ctx = _ctx_for(runner, [StepItem("s", list(range(17, n)), [])])
+    b = mixer.forward(x[17:], ctx, view)
+    assert torch.equal(torch.cat([a, b]), got)
+
+
+def test_block_part_alone(cuda_device, tmp_path):
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.parts import ResidualStream
+    model, runner, d = _tiny_runner("B", tmp=tmp_path)
+    raw, w = H.read_model_dir(d)
+    c = P.read_config(raw)
+    n = 21
+    x = torch.randn(n, 96, device=cuda_device)
+    want = P.decoder_layer(x.double().cpu(), {k: v.double() for k, v in w.items()}, 2, c,
+                           torch.arange(n))
+    runner.add_request("r")
+    ctx = _ctx_for(runner, [StepItem("r", list(range(n)), [])])
+    stream = ResidualStream(x.clone())
+    model.blocks[2].forward(stream, ctx, runner.views[2])
+    stream.flush()
+    assert H.rel_err(stream.x.cpu(), want) < 5e-6
+
+
+# --------------------------------------------- parts and models defined by the test
+@dataclass(frozen=True)
+class DecaySpec:
+    kind: str = "test_decay_mixer"
+    decay: float = 0.9
+
+
+def _register_toy_parts():
+    """A mixer with fixed-size state per request (an exponentially decaying sum of the
+    projected inputs), a feed-forward with top-1 routing over two experts, and a position
+    encoding that adds a learned vector per position bucket; plain tensor code, float32."""
+    from binfer_b200.cache import StateNeed
+    from binfer_b200.parts import (FeedForward, Mixer, register_ffn, register_mixer,
+                                   register_position)
+    from binfer_b200.weights import ParamSpec
+
+    class DecayMixer(Mixer):
+        def __init__(self, spec, hidden, prefix, env):
+            self.spec, self.hidden, self.prefix, self.env = spec, hidden, prefix, env
+
+        def param_specs(self):
+            return [ParamSpec(self.prefix + "in.weight", (self.hidden, self.hidden))]
+
+        def load(self, get):
+            self.w = get(self.param_specs()[0])
+
+        def state_need(self):
+            return StateNeed((self.hidden,), "float32")
+
+        def forward(self, x, ctx, view):
+            u = x.float() @ self.w.float().T
+            out = torch.empty_like(u)
+            starts = ctx.q_start.tolist()
+            slots = ctx.state_slots.tolist()
+            for b in range(ctx.B):
+                s = view.state[slots[b]]
+                for t in range(starts[b], starts[b + 1]):
+                    s.mul_(self.spec.decay).add_(u[t])
+                    out[t] = s
+            return out.to(x.dtype)
+
+    @dataclass(frozen=True)
+    class RoutedSpec:
+        kind: str = "test_routed_ffn"
+        experts: int = 2
+
+    class RoutedFFN(FeedForward):
+        def __init__(self, spec, hidden, prefix, env):
+            self.spec, self.hidden, self.prefix = spec, hidden, prefix
+
+        def param_specs(self):
+            e = self.spec.experts
+            return [ParamSpec(self.prefix + "router.weight", (e, self.hidden)),
+                    ParamSpec(self.prefix + "experts.weight", (e * self.hidden, self.hidden))]
+
+        def load(self, get):
+            r, e = self.param_specs()
+            self.router, self.experts = get(r), get(e).view(self.spec.experts, self.hidden, -1)
+
+        def forward(self, x, ctx):
+            choice = (x.float() @ self.router.float().T).argmax(-1)      # router logits in float
+            return torch.einsum("th,thk->tk", x.float(),
+                                self.experts.float()[choice].transpose(1, 2)).to(x.dtype)
+
+    register_mixer("test_decay_mixer", DecayMixer)
+    register_ffn("test_routed_ffn", RoutedFFN)
+    return DecaySpec, RoutedSpec
+
+
+def _toy_spec(layers, schedule, vocab=50, hidden=32):
+    from binfer_b200.config import ModelSpec, NameLayout, NormSpec
+    return ModelSpec(architecture="ToyForCausalLM", hidden_size=hidden, vocab_size=vocab,
+                     layers=tuple(layers), schedule=tuple(schedule), final_norm=NormSpec(eps=1e-5),
+                     tie_word_embeddings=True, names=NameLayout())
+
+
+def test_toy_mixer_with_state_and_routed_ffn(cuda_device):
+    """Registered, built from specs, loaded by name, and stepped whole and in portions: the
+    carried state makes the portions agree with the whole."""
+    from binfer_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, NormSpec, RopeSpec,
+                                    ScheduleEntry, register_architecture, parse_config)
+    from binfer_b200.engine import make_runner
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.parts import build_model, param_specs_for
+    from binfer_b200.weights import TensorSource, random_tensors
+    DecaySpecT, RoutedSpecT = _register_toy_parts()
+    norm = NormSpec(eps=1e-5)
+    attn = AttentionSpec(num_heads=2, num_kv_heads=1, head_dim=16, position=RopeSpec(theta=100.0))
+    layers = [LayerSpec(mixer=DecaySpecT(decay=0.8), ffn=RoutedSpecT(), norm=norm),
+              LayerSpec(mixer=attn, ffn=GatedMLPSpec(intermediate_size=48), norm=norm),
+              LayerSpec(mixer=DecaySpecT(decay=0.5), ffn=GatedMLPSpec(intermediate_size=40), norm=norm)]
+    spec = _toy_spec(layers, [ScheduleEntry(i) for i in range(3)])
+    # a whole architecture, chosen by config.json's name like any other
+    register_architecture("ToyForCausalLM", lambda raw: type("C", (), {"to_spec": lambda self: spec})())
+    assert parse_config({"architectures": ["ToyForCausalLM"]}).to_spec() is spec
+    names = [s.name for s in param_specs_for(spec)]
+    assert "model.layers.0.self_attn.in.weight" in names
+    assert "model.layers.0.mlp.router.weight" in names
+    env = _env()
+    model = build_model(spec, env, TensorSource.from_dict(
+        random_tensors(param_specs_for(spec), seed=1, std=0.2, norm_std=0.05)))
+    assert [n is not None for n in model.kv_needs()] == [False, True, False]
+    assert [n is not None for n in model.state_needs()] == [True, False, True]
+    toks = H.random_tokens(23, 50, 3)
+
+    def run(cuts):
+        runner = make_runner(model, env, page_size=4, num_pages=16, max_requests=2)
+        runner.add_request("other")               # another request's state must not leak in
+        runner.step([StepItem("other", toks[::-1][:5], [])])
+        runner.add_request("r")
+        rows, a = [], 0
+        for n in cuts:
+            rows.append(runner.step([StepItem("r", toks[a:a + n], list(range(n)))]).clone())
+            a += n
+        return torch.cat(rows)
+
+    whole = run([23])
+    assert torch.isfinite(whole).all() and float(whole.abs().max()) > 0
+    parts = run([7, 1, 2, 13])
+    assert H.rel_err(parts, whole) < 1e-5
+    # a slot that is handed out again starts from zero state
+    runner = make_runner(model, env, page_size=4, num_pages=16, max_requests=1)
+    runner.add_request("a")
+    first = runner.step([StepItem("a", toks, [22])]).clone()
+    runner.free_request("a")
+    runner.add_request("b")
+    assert torch.equal(runner.step([StepItem("b", toks, [22])]), first)
+
+
+def test_schedule_runs_a_layer_twice_and_shares_pages(cuda_device):
+    """The order of execution is data: layer 0 runs twice (two caches of its own), and the
+    last entry reads the pages that the first one wrote."""
+    from binfer_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, NormSpec, RopeSpec,
+                                    ScheduleEntry)
+    from binfer_b200.engine import make_runner
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.parts import build_model, param_specs_for
+    from binfer_b200.weights import TensorSource, random_tensors
+    norm = NormSpec(eps=1e-6)
+    attn = AttentionSpec(num_heads=4, num_kv_heads=2, head_dim=8, qk_norm=True,
+                         position=RopeSpec(theta=1000.0))
+    layer = LayerSpec(mixer=attn, ffn=GatedMLPSpec(intermediate_size=24), norm=norm)
+    sched = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_from=0)]
+    spec = _toy_spec([layer, layer], sched, vocab=40, hidden=32)
+    env = _env()
+    weights = random_tensors(param_specs_for(spec), seed=4, std=0.3, norm_std=0.05)
+    model = build_model(spec, env, TensorSource.from_dict(weights))
+    assert [n is not None for n in model.kv_needs()] == [True, True, True, False]
+    toks = H.random_tokens(19, 40, 8)
+
+    # plain restatement of this schedule from the plain parts
+    w = {k: v.double() for k, v in weights.items()}
+    c = dict(heads=4, kv_heads=2, head_dim=8, eps=1e-6, theta=1000.0, factor=1.0)
+    pos = torch.arange(19)
+    x = P.embedding(torch.tensor(toks), w["model.embed_tokens.weight"])
+    k0 = v0 = None
+    for e, entry in enumerate(sched):
+        p = f"model.layers.{entry.layer}."
+        n = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6)
+        a = p + "self_attn."
+        q = P.rms_norm((n @ w[a + "q_proj.weight"].T).view(19, 4, 8), w[a + "q_norm.weight"], 1e-6)
+        k = P.rms_norm((n @ w[a + "k_proj.weight"].T).view(19, 2, 8), w[a + "k_norm.weight"], 1e-6)
+        v = (n @ w[a + "v_proj.weight"].T).view(19, 2, 8)
+        ang = P.rope_angles(pos, 8, 1000.0)
+        q, k = P.apply_rope(q, ang), P.apply_rope(k, ang)
+        if e == 0:
+            k0, v0 = k, v
+        if entry.cache_from is not None:
+            k, v = k0, v0
+        att = P.causal_attention(q, k, v, 8 ** -0.5).reshape(19, 32) @ w[a + "o_proj.weight"].T
+        x = x + att
+        n = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6)
+        x = x + P.swiglu_mlp(n, w, p + "mlp.")
+    want = P.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+    for cuts in ([19], [5, 1, 1, 12]):
+        runner = make_runner(model, env, page_size=4, num_pages=8, max_requests=2)
+        runner.add_request("r")
+        rows, a = [], 0
+        for n in cuts:
+            rows.append(runner.step([StepItem("r", toks[a:a + n], list(range(n)))]).clone())
+            a += n
+        assert H.rel_err(torch.cat(rows).cpu(), want) < 2e-5, cuts
