@@ -227,7 +227,11 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ q,
   }
 }
 
-// Merge the splits of each (row, head) in ascending order and normalise.
+// Merge the splits of each (row, head) in ascending order and normalise.  One block per
+// (row, head): the splits' maxima and sums are reduced by the first warp, each split's
+// weight exp2(m_s - M) is parked in shared memory, and every thread then walks the splits
+// for its output columns with several loads in flight.
+#define MERGE_CHUNK 256
 template <int D>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ part_o,
                                               const float* __restrict__ part_ml,
@@ -235,23 +239,63 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ part_o,
                                               const int* __restrict__ positions,
                                               __nv_bfloat16* __restrict__ out, int nh, int window,
                                               int max_splits) {
+  __shared__ float wgt[MERGE_CHUNK];
+  __shared__ float sh_M, sh_L;
   const int r = blockIdx.x, h = blockIdx.y;
   const int t = rows ? rows[r] : r;
   const int p = positions[t];
   const int j0 = window > 0 ? max(0, p - window + 1) : 0;
   const int s_first = j0 / DEC_SPLIT, s_last = p / DEC_SPLIT;
   const size_t base = ((size_t)r * nh + h) * max_splits;
-  float M = -INFINITY;
-  for (int s = s_first; s <= s_last; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f;
-  for (int s = s_first; s <= s_last; ++s)
-    L += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - M);
-  const float inv = 1.f / L;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    float acc = 0.f;
-    for (int s = s_first; s <= s_last; ++s)
-      acc += part_o[(base + s) * D + c] * exp2f(part_ml[(base + s) * 2] - M);
-    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(acc * inv);
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    float M = -INFINITY;
+    for (int s = s_first + lane; s <= s_last; s += 32) M = fmaxf(M, __ldcg(part_ml + (base + s) * 2));
+    M = warp_max(M);
+    float L = 0.f;      // lanes sum disjoint splits; the order of this sum is fixed by (p, window)
+    for (int s = s_first + lane; s <= s_last; s += 32)
+      L += __ldcg(part_ml + (base + s) * 2 + 1) * exp2f(__ldcg(part_ml + (base + s) * 2) - M);
+    L = warp_sum(L);
+    if (lane == 0) {
+      sh_M = M;
+      sh_L = L;
+    }
+  }
+  __syncthreads();
+  const float M = sh_M, inv = 1.f / sh_L;
+  float acc[(D + 127) / 128];
+#pragma unroll
+  for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = 0.f;
+  for (int c0 = s_first; c0 <= s_last; c0 += MERGE_CHUNK) {
+    const int n = min(MERGE_CHUNK, s_last - c0 + 1);
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+      wgt[i] = exp2f(__ldcg(part_ml + (base + c0 + i) * 2) - M);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < (D + 127) / 128; ++i) {
+      const int c = threadIdx.x + i * 128;
+      if (c < D) {
+        const float* po = part_o + (base + c0) * D + c;
+        float a = acc[i];
+        int s = 0;
+        for (; s + 4 <= n; s += 4) {
+          const float v0 = __ldcg(po + (size_t)s * D), v1 = __ldcg(po + (size_t)(s + 1) * D);
+          const float v2 = __ldcg(po + (size_t)(s + 2) * D), v3 = __ldcg(po + (size_t)(s + 3) * D);
+          a += v0 * wgt[s];
+          a += v1 * wgt[s + 1];
+          a += v2 * wgt[s + 2];
+          a += v3 * wgt[s + 3];
+        }
+        for (; s < n; ++s) a += __ldcg(po + (size_t)s * D) * wgt[s];
+        acc[i] = a;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < (D + 127) / 128; ++i) {
+    const int c = threadIdx.x + i * 128;
+    if (c < D) out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(acc[i] * inv);
   }
 }
 
@@ -281,7 +325,7 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
       num_pages, window, max_splits, scale * 1.4426950408889634f, err);
   int e = bf_launch_status();
   if (e) return e;
-  decode_attention_merge_kernel<D><<<dim3(n_rows, nh), D >= 128 ? 128 : 64, 0, stream>>>(
+  decode_attention_merge_kernel<D><<<dim3(n_rows, nh), 128, 0, stream>>>(
       part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);
   return bf_launch_status();
 }

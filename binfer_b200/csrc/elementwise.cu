@@ -71,10 +71,86 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
   for (int c = threadIdx.x; c < H; c += blockDim.x) bf_st(o + c, row[c] * inv * w[c]);
 }
 
+// The same for bf16 activations and H a multiple of 8: 8 elements per thread per trip, all
+// loads of a trip issued before they are used, the row kept in registers between the passes.
+template <int TRIPS>
+__global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid,
+                                            const __nv_bfloat16* __restrict__ delta,
+                                            const float* __restrict__ w,
+                                            __nv_bfloat16* __restrict__ out,
+                                            const int* __restrict__ rows, int H, float eps,
+                                            int write_back) {
+  __shared__ float scratch[33];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* x = resid + (size_t)r * H;
+  const __nv_bfloat16* d = delta ? delta + (size_t)r * H : nullptr;
+  float v[TRIPS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < TRIPS; ++k) {
+    const int c = (k * blockDim.x + threadIdx.x) * 8;
+    if (c < H) {
+      const float4 a = *reinterpret_cast<const float4*>(x + c);
+      const float4 b = *reinterpret_cast<const float4*>(x + c + 4);
+      v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
+      v[k][4] = b.x; v[k][5] = b.y; v[k][6] = b.z; v[k][7] = b.w;
+      if (d) {
+        const uint4 q = *reinterpret_cast<const uint4*>(d + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          v[k][2 * j] += f.x;
+          v[k][2 * j + 1] += f.y;
+        }
+        if (write_back) {
+          *reinterpret_cast<float4*>(x + c) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+          *reinterpret_cast<float4*>(x + c + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  __nv_bfloat16* o = out + (size_t)i * H;
+#pragma unroll
+  for (int k = 0; k < TRIPS; ++k) {
+    const int c = (k * blockDim.x + threadIdx.x) * 8;
+    if (c < H) {
+      const float4 wa = *reinterpret_cast<const float4*>(w + c);
+      const float4 wb = *reinterpret_cast<const float4*>(w + c + 4);
+      uint4 q;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+      h[0] = __floats2bfloat162_rn(v[k][0] * inv * wa.x, v[k][1] * inv * wa.y);
+      h[1] = __floats2bfloat162_rn(v[k][2] * inv * wa.z, v[k][3] * inv * wa.w);
+      h[2] = __floats2bfloat162_rn(v[k][4] * inv * wb.x, v[k][5] * inv * wb.y);
+      h[3] = __floats2bfloat162_rn(v[k][6] * inv * wb.z, v[k][7] * inv * wb.w);
+      *reinterpret_cast<uint4*>(o + c) = q;
+    }
+  }
+}
+
 BF_EXPORT int bf_add_rmsnorm(float* resid, const void* delta, const float* w, void* out,
                              const int* rows, int n_rows, int H, float eps, int act_dtype,
                              int write_back, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (act_dtype == BF_DTYPE_BF16 && H % 8 == 0 && H <= 8 * 256 * 4 &&
+      ((uintptr_t)resid & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
+      ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const int threads = H >= 2048 ? 256 : 128;
+    const int trips = (H / 8 + threads - 1) / threads;
+    auto args = [&](auto kern) {
+      kern<<<n_rows, threads, 0, stream>>>(resid, (const __nv_bfloat16*)delta, w,
+                                           (__nv_bfloat16*)out, rows, H, eps, write_back);
+    };
+    if (trips <= 1) args(add_rmsnorm_bf16_vec_kernel<1>);
+    else if (trips == 2) args(add_rmsnorm_bf16_vec_kernel<2>);
+    else args(add_rmsnorm_bf16_vec_kernel<4>);
+    return bf_launch_status();
+  }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const size_t smem = (size_t)(H + 33) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
