@@ -359,6 +359,28 @@ BF_EXPORT int bf_decode_attention(const void* q, const void* k_cache, const void
 
 BF_EXPORT int bf_decode_attention_split_keys() { return DEC_SPLIT; }
 
+// Only the second half: merge the partials that a split kernel left in scratch.
+BF_EXPORT int bf_decode_attention_merge(const float* part_o, const float* part_ml, const int* rows,
+                                        const int* positions, void* out, int n_rows, int nh, int d,
+                                        int window, int max_splits, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+#define BF_MERGE_CASE(DD)                                                                  \
+  case DD:                                                                                 \
+    decode_attention_merge_kernel<DD><<<dim3(n_rows, nh), 128, 0, stream>>>(               \
+        part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);    \
+    return bf_launch_status()
+  switch (d) {
+    BF_MERGE_CASE(32);
+    BF_MERGE_CASE(64);
+    BF_MERGE_CASE(96);
+    BF_MERGE_CASE(128);
+    BF_MERGE_CASE(256);
+    default:
+      return (int)cudaErrorInvalidValue;
+  }
+#undef BF_MERGE_CASE
+}
+
 // ------------------------------------------------------------------------------
 // The same attention with its scratch inside the library (see the header for who
 // needs this and for the rules of use).  Host code must not pass the array's

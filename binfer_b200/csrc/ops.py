@@ -193,22 +193,31 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      rows: Optional[torch.Tensor], n_rows: int, seq_of_token: torch.Tensor,
                      positions: torch.Tensor, block_tables: torch.Tensor, out: torch.Tensor,
                      nh: int, nkv: int, d: int, window: Optional[int], scale: float,
-                     max_ctx_len: int, err: torch.Tensor) -> None:
+                     max_ctx_len: int, err: torch.Tensor, variant: str = "auto") -> None:
     """Split-KV attention for rows that bring one token each (bfloat16 only).
 
     ``rows`` lists the token rows to run (None: rows 0..n_rows-1); ``max_ctx_len``
     bounds the context of every such row.  Scratch for the splits' partial results
-    is taken from torch's allocator."""
+    is taken from torch's allocator.  ``variant``: ``tma`` (bulk tensor copies; head
+    sizes 64/128/256, page sizes 8..128 that divide 128), ``cp_async`` (every size in
+    DECODE_HEAD_DIMS, any page size), or ``auto``: tma where it applies."""
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"decode_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
+    page_size = k_cache.shape[2]
+    tma_ok = d in (64, 128, 256) and 8 <= page_size <= 128 and 128 % page_size == 0
+    if variant == "tma" and not tma_ok:
+        raise KernelError(f"decode_attention: the tma variant does not take head_dim {d} with "
+                          f"pages of {page_size}")
+    use_tma = tma_ok and variant != "cp_async"
     max_splits = max(1, -(-int(max_ctx_len) // DECODE_SPLIT_KEYS))
     part_o = torch.empty((n_rows, nh, max_splits, d), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_rows, nh, max_splits, 2), dtype=torch.float32, device=q.device)
-    _run("decode_attention", lib().bf_decode_attention,
+    fn = lib().bf_decode_attention_tma if use_tma else lib().bf_decode_attention
+    _run("decode_attention_tma" if use_tma else "decode_attention", fn,
          _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(rows), _ptr(seq_of_token), _ptr(positions),
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _ptr(part_o),
          _ptr(part_ml), _c_int(n_rows), _c_int(nh), _c_int(nkv), _c_int(d),
-         _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]), _c_int(window or 0),
+         _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
          _c_int(max_splits), _c_float(scale), _ptr(err), _stream())
     global _launches
     _launches += 1          # two kernels: the splits and their merge

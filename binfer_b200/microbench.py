@@ -90,7 +90,8 @@ def decode_attention(a):
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
     err = ops.error_word(dev)
     fns = [lambda c=c: ops.decode_attention(q, c[0], c[1], None, B, sot, pos, c[2], out, nh, nkv, d,
-                                            None, d ** -0.5, ctx, err) for c in caches]
+                                            None, d ** -0.5, ctx, err, variant=a.variant)
+           for c in caches]
     us = timed(fns, a.iters, a.warmup)
     report("decode_attention", us, nbytes=per_set, batch=B, ctx=ctx, heads=nh, kv_heads=nkv,
            head_dim=d, page_size=ps)
@@ -161,6 +162,8 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0, help="feature rows per tile (0: chosen)")
     ap.add_argument("--library", action="store_true", help="time cuBLAS on the same product")
+    ap.add_argument("--variant", default="auto", choices=["auto", "tma", "cp_async"],
+                    help="how the decode attention fetches its tiles")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)

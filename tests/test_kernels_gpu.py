@@ -213,9 +213,13 @@ def test_paged_attention_generic(cuda_device, dtype, nh, nkv, d, ps, window, spi
     (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
     (32, 8, 128, 16, None, False), (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 200, True),
     (2, 1, 256, 16, 100, True), (20, 1, 64, 16, None, True), (4, 4, 128, 64, 130, True)])
-def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike):
-    """Contexts on both sides of the 128-key split edge, and long ones."""
+@pytest.mark.parametrize("variant", ["cp_async", "tma"])
+def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike, variant):
+    """Contexts on both sides of the 128-key split edge, and long ones; both ways of
+    fetching the tiles."""
     from binfer_b200.csrc import ops
+    if variant == "tma" and not (d in (64, 128, 256) and ps >= 8 and 128 % ps == 0):
+        pytest.skip("the tma variant does not take this head or page size")
     ctxs = [1, 127, 128, 129, 300, 1000, 45]
     qlens = [1] * len(ctxs)
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
@@ -223,14 +227,14 @@ def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike):
     out = torch.zeros_like(q)
     err = _err(cuda_device)
     ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, window,
-                         d ** -0.5, max(ctxs) + 500, err)
+                         d ** -0.5, max(ctxs) + 500, err, variant=variant)
     assert int(err.item()) == 0
     _close(out, ref, BF16)
     # a subset of rows, given by index, gives the same bits for those rows
     rows = torch.tensor([5, 2, 4], dtype=torch.int32, device=cuda_device)
     out2 = torch.zeros_like(q)
     ops.decode_attention(q, kc, vc, rows, 3, sot, pos, bt, out2, nh, nkv, d, window,
-                         d ** -0.5, max(ctxs), err)
+                         d ** -0.5, max(ctxs), err, variant=variant)
     for r in (5, 2, 4):
         assert torch.equal(out2[r], out[r])
     assert float(out2[0].abs().max()) == 0.0

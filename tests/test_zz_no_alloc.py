@@ -61,7 +61,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(cuda_device):
         max_splits = -(-max(ctxs) // 128)
         want = torch.zeros_like(q)
         ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, want, nh, nkv, d, window,
-                             d ** -0.5, max(ctxs), err)
+                             d ** -0.5, max(ctxs), err, variant="cp_async")
         got = torch.zeros_like(q)
         code = _call_static(lib, q, kc, vc, None, len(ctxs), sot, pos, bt, got, nh, nkv, d,
                             window, max_splits, err)
