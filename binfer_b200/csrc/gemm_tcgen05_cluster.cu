@@ -1,0 +1,317 @@
+// bf16 matrix product for few tokens (at most 16) against a weight too narrow to give every
+// SM a tile: out[t, f] = sum_k x[t, k] * w[f, k], with the K range split over a thread-block
+// cluster and the partial sums combined through distributed shared memory.
+//
+// Why: a tcgen05.mma with M = 128 occupies the tensor pipe for about 128 cycles however
+// small N is, so a CTA only streams weights at the rate HBM can deliver when each product
+// covers many weight rows (N = 192..256 feature rows = 6..8 KB per product).  A projection
+// with 4096 or 6144 output features then has only 16 to 32 tiles for 148 SMs.  Here a
+// cluster of C CTAs (2, 4 or 8) shares one tile: CTA r of the cluster multiplies the r-th
+// part of the K range, so C times as many SMs stream.  The reference has no counterpart:
+// it calls cuBLAS for every product (cuda/kernels/gemm.cu:244-267).
+//
+// Per CTA: warp 2 issues the TMA loads (token tile + BN x 64 weight tile per stage, 128-byte
+// swizzle), warp 1 issues tcgen05.mma into one TMEM accumulator, warp 0 (which may read TMEM
+// lanes 0..31; the tokens are rows 0..15) reads the accumulator.  Reduction: the tile's columns are cut
+// into C slices; CTA r owns slice r.  Every CTA writes each slice of its partial sum into
+// the owner's shared memory (st.shared::cluster), the cluster synchronises once
+// (barrier.cluster), and each owner adds the C partials of its slice in ascending rank
+// order and stores the result: one fixed order of summation, no atomics, no global
+// workspace, and nothing spins on another CTA (the cluster barrier is the hardware's).
+//
+// mbarrier waits are bounded (about a second); on a timeout the CTA sets BF_ERR_WAIT,
+// still contributes (zeros) and still joins the cluster barrier, frees TMEM and returns.
+// No TMA load uses multicast; every load reads this GPU's own memory.
+#include <cuda.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "tma_utils.cuh"
+#include "umma_utils.cuh"
+
+namespace {
+
+constexpr int CL_MAX_STAGES = 16;
+constexpr int CL_TOKENS = 16;                 // token rows fetched and reduced
+constexpr int CL_BAR_BYTES = 512;
+
+struct ClusterGemmParams {
+  int tokens, features, K;
+  int bn;                       // feature rows per tile (multiple of 16 * cluster)
+  int cluster;                  // CTAs per tile
+  int stages;
+  long long ldo;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
+               ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(96, 1)
+gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
+                    const ClusterGemmParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base);
+  uint64_t* empty = full + CL_MAX_STAGES;
+  uint64_t* acc_full = empty + CL_MAX_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // recv[rank][token][slice column]: partial sums sent to this CTA, as the owner of a slice
+  float* recv = reinterpret_cast<float*>(base + CL_BAR_BYTES);
+  const int slice = p.bn / p.cluster;                          // columns owned per CTA
+  const int recv_bytes = p.cluster * CL_TOKENS * slice * 4;
+  uint8_t* tiles = base + CL_BAR_BYTES + ((recv_bytes + 1023) & ~1023);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_rank();
+  const int tile = blockIdx.x / p.cluster;
+  const int kc_total = (p.K + BK - 1) / BK;
+  const int kc0 = (int)((long long)kc_total * rank / p.cluster);
+  const int kc1 = (int)((long long)kc_total * (rank + 1) / p.cluster);
+  const int a_bytes = CL_TOKENS * BK * 2, b_bytes = p.bn * BK * 2;
+  const int stage_bytes = a_bytes + b_bytes;
+  const int STAGES = p.stages;
+  constexpr int TMEM_COLS = 256;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 2) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kc = kc0; kc < kc1; ++kc) {
+        if (!mbar_wait(empty + stage, phase ^ 1, abort)) break;
+        uint8_t* dst = tiles + (size_t)stage * stage_bytes;
+        mbar_expect_tx(full + stage, stage_bytes);
+        tma_load_2d(dst, &map_x, full + stage, kc * BK, 0);
+        tma_load_2d(dst + a_bytes, &map_w, full + stage, kc * BK, tile * p.bn);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && kc1 > kc0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                             ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kc = kc0; kc < kc1; ++kc) {
+        if (!mbar_wait(full + stage, phase, abort)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + (size_t)stage * stage_bytes);
+        const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+        const uint64_t b_desc = umma_desc_k_sw128(a_addr + a_bytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_bf16(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                    (kc > kc0 || k > 0) ? 1u : 0u);
+        umma_commit(empty + stage);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // warp 0: TMEM lanes 0..31; lane l holds token l of the partial sum
+    bool have = kc1 > kc0;
+    if (have) have = mbar_wait(acc_full, 0, abort);
+    have = __all_sync(0xffffffffu, have);
+    tc_fence_after();
+    const uint32_t my_recv = smem_u32(recv);
+    for (int c0 = 0; c0 < p.bn; c0 += 16) {
+      uint32_t r[16];
+      if (have) {
+        tmem_ld16(tmem_base + c0, r);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0u;     // no K steps here (or a timeout): send zeros
+      }
+      if (lane < CL_TOKENS) {
+        const int owner = c0 / slice, col = c0 - owner * slice;
+        const uint32_t dst = map_to_rank(
+            my_recv + (uint32_t)(((rank * CL_TOKENS + lane) * slice + col) * 4), (uint32_t)owner);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          st_cluster_v4(dst + 16 * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+      }
+    }
+    tc_fence_before();
+  }
+
+  // every thread of every CTA of the cluster: partials are in place after this
+  cluster_sync_all();
+
+  // this CTA's slice: add the partials in ascending rank order, store
+  for (int idx = threadIdx.x; idx < p.tokens * slice; idx += blockDim.x) {
+    const int t = idx / slice, col = idx - t * slice;
+    float sum = 0.f;
+    for (int r = 0; r < p.cluster; ++r) sum += recv[(r * CL_TOKENS + t) * slice + col];
+    const int f = tile * p.bn + rank * slice + col;
+    if (f < p.features) bf_st(out + (size_t)t * p.ldo + f, sum);
+  }
+
+  __syncthreads();
+  if (*abort && threadIdx.x == 0) atomicOr(p.err, BF_ERR_WAIT);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+  // no CTA may exit while a peer could still write into its shared memory: all writes
+  // happened before the cluster barrier above, so nothing more is needed here
+}
+
+template <typename OutT>
+int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p, long long ldx,
+                   long long ldw, cudaStream_t stream) {
+  CUtensorMap mx, mw;
+  int e = bf_make_tensor_map_bf16_2d(&mx, x, p.tokens, p.K, ldx, CL_TOKENS, BK);
+  if (e) return e;
+  e = bf_make_tensor_map_bf16_2d(&mw, w, p.features, p.K, ldw, p.bn, BK);
+  if (e) return e;
+  const size_t smem_max = 226 * 1024;
+  const size_t stage_bytes = (size_t)(CL_TOKENS + p.bn) * BK * 2;
+  const size_t recv_bytes = ((size_t)CL_TOKENS * p.bn * 4 + 1023) & ~(size_t)1023;
+  // behind the last stage the MMA still reads 128 token rows' worth of shared memory
+  const size_t fixed = 1024 + CL_BAR_BYTES + recv_bytes + 16 * 1024;
+  int stages = (int)((smem_max - fixed) / stage_bytes);
+  if (stages > CL_MAX_STAGES) stages = CL_MAX_STAGES;
+  if (stages < 2) return (int)cudaErrorInvalidValue;
+  p.stages = stages;
+  const size_t smem = fixed + (size_t)stages * stage_bytes;
+  auto kern = gemm_cluster_kernel<OutT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem_max);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  const int tiles = (p.features + p.bn - 1) / p.bn;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * p.cluster, 1, 1);
+  cfg.blockDim = dim3(96, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, mx, mw, out, p);
+  if (ce != cudaSuccess) return (int)ce;
+  return bf_launch_status();
+}
+
+}  // namespace
+
+// Tile width and cluster size for `features` x K on `num_sms` SMs.  Clusters of 4 measured
+// best on a B200 (8 schedules worse, 2 leaves too few CTAs); the tile width (a multiple of
+// 16 per CTA of the cluster, at most 256 feature rows) is the one that brings the number of
+// CTAs closest to, and not above, the SM count, each CTA keeping at least 4 K-steps.
+// Returns the number of CTAs, or 0 (outputs untouched) when no split is worth it.
+BF_EXPORT int bf_gemm_cluster_plan(int features, int K, int num_sms, int* bn_out,
+                                   int* cluster_out) {
+  const int kc = (K + BK - 1) / BK;
+  int best_ctas = 0, best_bn = 0, best_c = 0;
+  const int order[2] = {4, 2};
+  for (int i = 0; i < 2; ++i) {
+    const int c = order[i];
+    if (kc / c < 4) continue;
+    const int max_ctas = (num_sms / c) * c;
+    for (int bn = 256; bn >= 64; bn -= 16) {
+      if (bn % (16 * c)) continue;
+      const int ctas = ((features + bn - 1) / bn) * c;
+      if (ctas > max_ctas) continue;
+      if (ctas > best_ctas) {
+        best_ctas = ctas;
+        best_bn = bn;
+        best_c = c;
+      }
+    }
+  }
+  if (best_ctas == 0) return 0;
+  *bn_out = best_bn;
+  *cluster_out = best_c;
+  return best_ctas;
+}
+
+// out[tokens, features] = x[tokens, K] * w[features, K]^T for tokens <= 16, the K range split
+// over clusters of `cluster` CTAs.  bn: feature rows per tile, a multiple of 16 * cluster,
+// at most 256.  Returns cudaErrorInvalidValue for what it does not take.
+BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int tokens,
+                                   int features, int K, long long ldx, long long ldw,
+                                   long long ldo, int out_dtype, int bn, int cluster, int* err,
+                                   cudaStream_t stream) {
+  if (tokens <= 0 || features <= 0) return 0;
+  if (tokens > CL_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
+      ((uintptr_t)w & 15))
+    return (int)cudaErrorInvalidValue;
+  if ((cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
+      bn % (16 * cluster))
+    return (int)cudaErrorInvalidValue;
+  ClusterGemmParams p;
+  p.tokens = tokens;
+  p.features = features;
+  p.K = K;
+  p.bn = bn;
+  p.cluster = cluster;
+  p.stages = 0;
+  p.ldo = ldo;
+  p.err = err;
+  return out_dtype == BF_DTYPE_F32
+             ? launch_cluster<float>(x, w, (float*)out, p, ldx, ldw, stream)
+             : launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)out, p, ldx, ldw, stream);
+}

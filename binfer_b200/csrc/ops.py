@@ -292,6 +292,34 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: torch.Te
     return True
 
 
+def gemm_cluster_plan(features: int, K: int, device: torch.device):
+    """(bn, cluster) for the split-K cluster product, or None when it does not apply."""
+    sms = _num_sms.get(device.index)
+    if sms is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _num_sms[device.index] = sms
+    bn, c = _c_int(0), _c_int(0)
+    n = lib().bf_gemm_cluster_plan(_c_int(features), _c_int(K), _c_int(sms), ctypes.byref(bn),
+                                   ctypes.byref(c))
+    return (bn.value, c.value) if n > 0 else None
+
+
+def gemm_bf16_cluster(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
+                      bn: int, cluster: int) -> bool:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 16 with the K range split over clusters of
+    ``cluster`` CTAs (partials combined through distributed shared memory).  Returns False,
+    having done nothing, for shapes the kernel does not take."""
+    M, K = x.shape
+    N = w.shape[0]
+    if (M > 16 or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
+            or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or out.stride(1) != 1):
+        return False
+    _run("gemm_bf16_cluster", lib().bf_gemm_bf16_cluster, _ptr(x), _ptr(w), _ptr(out), _c_int(M),
+         _c_int(N), _c_int(K), _c_ll(x.stride(0)), _c_ll(w.stride(0)), _c_ll(out.stride(0)),
+         _c_int(_dtype_code(out)), _c_int(bn), _c_int(cluster), _ptr(err), _stream())
+    return True
+
+
 # -------------------------------------------------------------------- sampling
 def repetition_penalty(logits: torch.Tensor, items: torch.Tensor, penalty: torch.Tensor) -> None:
     """items: int32 [n, 3] of (row, token, count)."""

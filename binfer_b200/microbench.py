@@ -37,16 +37,32 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+GRAPH = True
+
+
 def timed(fns, iters, warmup):
-    """Microseconds per call of fns[i % len(fns)]() (a rotation of input sets)."""
-    for i in range(warmup):
+    """Microseconds per call of fns[i % len(fns)]() (a rotation of input sets).  The calls
+    are captured into one CUDA graph, as the engine's decode step is, so that the host's
+    launch cost does not hide the time of a short kernel."""
+    for i in range(max(warmup, 1)):
         fns[i % len(fns)]()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(iters):
-        fns[i % len(fns)]()
-    b.record()
+    if GRAPH and iters > 1:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fns[i % len(fns)]()
+        g.replay()
+        torch.cuda.synchronize()
+        a.record()
+        g.replay()
+        b.record()
+    else:
+        a.record()
+        for i in range(iters):
+            fns[i % len(fns)]()
+        b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) * 1e3 / iters
 
@@ -122,12 +138,17 @@ def gemm(a):
     x = torch.randn(M, K, device=dev).to(BF16)
     out = torch.empty(M, N, device=dev, dtype=BF16)
     err = ops.error_word(dev)
+    name = "gemm_bf16_tcgen05"
     if a.library:
+        name = "gemm_library"
         fns = [lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]
+    elif a.cluster:
+        name = f"gemm_bf16_cluster(bn={a.bn},cluster={a.cluster})"
+        fns = [lambda w=w: ops.gemm_bf16_cluster(x, w, out, err, a.bn, a.cluster) for w in ws]
     else:
         fns = [lambda w=w: ops.gemm_bf16(x, w, out, err, bn=a.bn) for w in ws]
     us = timed(fns, a.iters, a.warmup)
-    report("gemm_library" if a.library else "gemm_bf16_tcgen05", us,
+    report(name, us,
            nbytes=(N * K + M * K + M * N) * 2, flops=2.0 * M * N * K, tokens=M, features=N, k=K)
 
 
@@ -162,6 +183,9 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0, help="feature rows per tile (0: chosen)")
     ap.add_argument("--library", action="store_true", help="time cuBLAS on the same product")
+    ap.add_argument("--cluster", type=int, default=0,
+                    help="gemm: split K over clusters of this many CTAs (needs --bn)")
+    ap.add_argument("--no-graph", action="store_true", help="launch from the host, no CUDA graph")
     ap.add_argument("--variant", default="auto", choices=["auto", "tma", "cp_async"],
                     help="how the decode attention fetches its tiles")
     a = ap.parse_args(argv)
@@ -169,6 +193,8 @@ def main(argv=None):
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     ops.lib()
+    global GRAPH
+    GRAPH = not a.no_graph
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention,
      "gemm": gemm, "add_rmsnorm": add_rmsnorm}[a.kernel](a)
     return 0

@@ -6,8 +6,10 @@ cuBLAS through ``torch.mm`` with float accumulation, the library call the refere
 makes for every dense product (cuda/kernels/gemm.cu:244-267: ``cublasGemmEx``, bf16
 in, ``CUBLAS_COMPUTE_32F``).  Which one: ``BINFER_B200_GEMM=own`` takes the engine's
 kernel for every shape it accepts, ``library`` never, and ``auto`` (the default)
-where it was measured to be at least as fast as the library on a B200: few tokens
-against a wide weight (the gate/up projection and the output head while decoding).
+where it was measured to be at least as fast as the library on a B200: at most 128
+tokens against a very wide weight (the output head while decoding), and at most 16
+tokens against a weight of at most 4096 output features, where the split-K cluster
+kernel (``csrc/gemm_tcgen05_cluster.cu``) runs (the output and down projections).
 """
 from __future__ import annotations
 
@@ -35,7 +37,16 @@ def _use_own(M: int, N: int, K: int) -> bool:
         return True
     if _POLICY == "library":
         return False
-    return M <= 128 and N >= 16384
+    return M <= 128 and N >= 65536
+
+
+def _use_cluster(M: int, N: int, K: int) -> bool:
+    if _POLICY == "library" or M > 16:
+        return False
+    return N <= 4096 and K >= 2048 if _POLICY == "auto" else N <= 8192
+
+
+_plans = {}
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -50,7 +61,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         return out
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
-    if _use_own(M, N, x.shape[1]):
+    K = x.shape[1]
+    if _use_cluster(M, N, K):
+        plan = _plans.get((N, K))
+        if plan is None:
+            plan = _plans[(N, K)] = ops.gemm_cluster_plan(N, K, x.device) or False
+        if plan:
+            if out is None:
+                out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+            if ops.gemm_bf16_cluster(x, w, out, ops.error_word(x.device), *plan):
+                return out
+    if _use_own(M, N, K):
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
         if ops.gemm_bf16(x, w, out, ops.error_word(x.device)):

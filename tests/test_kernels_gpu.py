@@ -388,3 +388,33 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
     ops.prefill_attention(q, kc, vc, items[1:3].contiguous(), 2, 37, bt, out2, nh, nkv, d,
                           window, d ** -0.5, err)
     assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K,bn,c", [(1, 300, 520, 64, 4), (8, 4096, 4096, 128, 4),
+                                        (16, 1000, 4104, 128, 8), (7, 6144, 4096, 192, 4),
+                                        (3, 256, 256, 256, 2), (16, 4096, 12288, 128, 4),
+                                        (5, 96, 64, 64, 4)])
+@pytest.mark.parametrize("out_dtype", [BF16, F32])
+def test_gemm_bf16_cluster_split_k(cuda_device, M, N, K, bn, c, out_dtype):
+    """K split over a cluster and reduced through distributed shared memory; widths and depths
+    that are no multiple of the tile, fewer K steps than CTAs in the cluster."""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(M * 3 + N)
+    x = torch.randn(M, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(BF16).to(cuda_device)
+    out = torch.full((M, N), 99.0, device=cuda_device, dtype=out_dtype)
+    err = ops.error_word(cuda_device)
+    assert ops.gemm_bf16_cluster(x, w, out, err, bn, c)
+    assert int(err.item()) == 0
+    ref = x.double().cpu() @ w.double().cpu().T
+    if out_dtype == BF16:
+        _close(out, ref, BF16)
+    else:
+        err_rel = float((out.double().cpu() - ref).abs().max() / ref.abs().max())
+        assert err_rel <= 4e-7 * math.sqrt(K), err_rel
+    again = torch.empty_like(out)
+    assert ops.gemm_bf16_cluster(x, w, again, err, bn, c)
+    assert torch.equal(again, out), "the split-K sum must have one fixed order"
+    assert not ops.gemm_bf16_cluster(torch.zeros(17, K, device=cuda_device, dtype=BF16), w,
+                                     torch.empty(17, N, device=cuda_device, dtype=out_dtype),
+                                     err, bn, c)
