@@ -245,7 +245,7 @@ def main():
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
-    h0, d0 = runner.h2d_bytes, sampler.d2h_bytes
+    h0, d0 = runner.h2d_bytes + sampler.h2d_bytes, sampler.d2h_bytes
     t1 = time.perf_counter()
     n_e2e = 0
     for _ in range(steps - 1):
@@ -253,7 +253,7 @@ def main():
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t1
     e2e = {"value": n_e2e / e2e_s, "unit": "tokens/s",
-           "h2d_bytes_per_step": (runner.h2d_bytes - h0) // max(steps - 1, 1),
+           "h2d_bytes_per_step": (runner.h2d_bytes + sampler.h2d_bytes - h0) // max(steps - 1, 1),
            "d2h_bytes_per_step": (sampler.d2h_bytes - d0) // max(steps - 1, 1)}
     while engine.has_work():
         engine.step()

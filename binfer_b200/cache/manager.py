@@ -51,6 +51,28 @@ class RequestCache:
     length: int = 0                            # tokens whose keys/values are cached
     tables: List[List[int]] = field(default_factory=list)   # per group: page id or -1
     fresh: bool = True                         # state slot not yet zeroed on the device
+    # per group: the table as an int32 array for the step's batch description, kept in step
+    # with `tables` (entries appended; rebuilt after a windowed page was released)
+    np_tables: List[object] = field(default_factory=list)
+    np_valid: List[int] = field(default_factory=list)
+
+    def table_array(self, g: int):
+        """``tables[g]`` as a numpy int32 array (a view of a cached buffer)."""
+        import numpy as np
+        table = self.tables[g]
+        n = len(table)
+        while len(self.np_tables) <= g:
+            self.np_tables.append(None)
+            self.np_valid.append(0)
+        arr, valid = self.np_tables[g], self.np_valid[g]
+        if arr is None or arr.shape[0] < n or valid < 0:
+            arr = np.zeros(max(16, 2 * n), dtype=np.int32)
+            arr[:n] = table
+            self.np_tables[g] = arr
+        elif valid < n:
+            arr[valid:n] = table[valid:n]
+        self.np_valid[g] = n
+        return arr[:n]
 
 
 class CacheGroup:
@@ -177,6 +199,8 @@ class CacheManager:
             if table[i] > 0:
                 g.pool.free(table[i])
                 table[i] = -1
+                if len(rc.np_valid) > g.index:
+                    rc.np_valid[g.index] = -1      # the cached array is stale
 
     def commit(self, rid: Hashable, new_len: int) -> None:
         """Record that the step wrote keys/values up to ``new_len``."""

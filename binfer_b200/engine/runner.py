@@ -145,9 +145,14 @@ class ModelRunner:
         t = r = 0
         for b, it in enumerate(items):
             n = q_lens[b]
-            tok[t:t + n] = np.asarray(it.tokens, dtype=np.int32)
-            pos[t:t + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
-            sot[t:t + n] = b
+            if n == 1:
+                tok[t] = it.tokens[0]
+                pos[t] = starts[b]
+                sot[t] = b
+            else:
+                tok[t:t + n] = it.tokens
+                pos[t:t + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
+                sot[t:t + n] = b
             qs[b] = t
             if not pad_to:
                 for w in it.want:
@@ -171,19 +176,23 @@ class ModelRunner:
         view("ctx_lens")[:] = ctx_lens
         view("state_slots")[:n_real] = [rc.slot for rc in rcs]
         for g in cache.groups:
-            w, ps = widths[g.index], g.page_size
-            sl = view(f"slots{g.index}")
-            tb = view(f"tables{g.index}").reshape(B, w)
+            gi, w, ps = g.index, widths[g.index], g.page_size
+            sl = view(f"slots{gi}")
+            tb = view(f"tables{gi}").reshape(B, w)
             t = 0
             for b, rc in enumerate(rcs):
-                table = np.asarray(rc.tables[g.index], dtype=np.int32)
+                table = rc.table_array(gi)
                 if len(table) > w:
                     raise ValueError(f"request {rc.rid!r} holds {len(table)} pages, the "
                                      f"block table has room for {w}")
                 tb[b, :len(table)] = table
-                p = np.arange(starts[b], ctx_lens[b])
-                sl[t:t + q_lens[b]] = table[p // ps] * ps + p % ps
-                t += q_lens[b]
+                n, start = q_lens[b], starts[b]
+                if n == 1:
+                    sl[t] = int(table[start // ps]) * ps + start % ps
+                else:
+                    p = np.arange(start, start + n)
+                    sl[t:t + n] = table[p // ps] * ps + p % ps
+                t += n
 
         if dev is None:
             dev = torch.empty(total, dtype=torch.int32, device=self.env.device)

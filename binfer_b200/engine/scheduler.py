@@ -119,16 +119,24 @@ class Scheduler:
                 self._finish(victim, "cache")
                 dropped.append(victim)
             else:
-                self._preempt(victim, [], [])
+                self._preempt(victim, [], [], [], [])
 
     def _plan(self, dropped: List[Request]) -> List[Scheduled]:
         plan: List[Scheduled] = []
         wants: List[Tuple[Hashable, int]] = []
+        costs: List[List[int]] = []          # pages each planned item adds, per cache group
+        need = [0] * len(self.cache.groups)  # their running total
         budget = self.max_tokens_per_step
         preemptions_before = self.num_preemptions
+        cache = self.cache
+
+        def cost_of(req: Request, n: int) -> List[int]:
+            return cache.pages_to_add(cache.get(req.rid), req.computed + n)
 
         def fits(req: Request, n: int, spare: int = 0) -> bool:
-            return self.cache.can_reserve(wants + [(req.rid, req.computed + n)], spare)
+            c = cost_of(req, n)
+            return all(g.pool.num_free - need[i] - c[i] >= spare
+                       for i, g in enumerate(cache.groups))
 
         def largest_fit(req: Request, n: int, spare: int = 0) -> int:
             """The longest portion <= n that fits, backing off page by page."""
@@ -139,9 +147,17 @@ class Scheduler:
 
         def take(req: Request, n: int) -> None:
             nonlocal budget
-            toks = req.all_tokens[req.computed:req.computed + n]
-            plan.append(Scheduled(req, toks, n == req.remaining))
+            total = len(req.prompt) + len(req.output)
+            if n == 1 and req.computed == total - 1:
+                toks = [req.output[-1] if req.output else req.prompt[-1]]
+            else:
+                toks = req.all_tokens[req.computed:req.computed + n]
+            plan.append(Scheduled(req, toks, req.computed + n == total))
             wants.append((req.rid, req.computed + n))
+            c = cost_of(req, n)
+            costs.append(c)
+            for i, v in enumerate(c):
+                need[i] += v
             budget -= n
 
         # 1. one token for every request that is decoding, oldest first
@@ -154,7 +170,7 @@ class Scheduler:
                     self._finish(req, "cache")
                     dropped.append(req)
                 else:
-                    budget += self._preempt(victim, plan, wants)
+                    budget += self._preempt(victim, plan, wants, costs, need)
             if req.state == RUNNING:
                 take(req, 1)
 
@@ -187,14 +203,18 @@ class Scheduler:
             take(req, n)
         return plan
 
-    def _preempt(self, req: Request, plan: List[Scheduled], wants: List) -> int:
+    def _preempt(self, req: Request, plan: List[Scheduled], wants: List, costs: List,
+                 need: List[int]) -> int:
         """Take ``req`` out of the running set and out of the plan; return the budget it frees."""
         freed = 0
         for i, s in enumerate(plan):
             if s.request is req:
                 freed = len(s.tokens)
+                for g, v in enumerate(costs[i]):
+                    need[g] -= v
                 del plan[i]
                 del wants[i]
+                del costs[i]
                 break
         self.cache.free_request(req.rid)
         self.running.remove(req)
