@@ -226,3 +226,18 @@ BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype
         (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
   return bf_launch_status();
 }
+
+// ------------------------------------------------------------- token ids from the device
+// dst[pairs[2i]] = src[pairs[2i+1]]: the ids that the last step sampled become this step's
+// input tokens without a trip through the host.
+__global__ void copy_ids_kernel(int* __restrict__ dst, const int* __restrict__ src,
+                                const int* __restrict__ pairs, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[pairs[2 * i]] = src[pairs[2 * i + 1]];
+}
+
+BF_EXPORT int bf_copy_ids(int* dst, const int* src, const int* pairs, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  copy_ids_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, src, pairs, n);
+  return bf_launch_status();
+}

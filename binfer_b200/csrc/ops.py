@@ -146,6 +146,12 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                              _c_int(_dtype_code(out)), _stream())
 
 
+def copy_ids(dst: torch.Tensor, src: torch.Tensor, pairs: torch.Tensor, n: int) -> None:
+    """dst[pairs[i, 0]] = src[pairs[i, 1]] for i < n (int32 everywhere)."""
+    _want(dst, torch.int32, "dst"); _want(src, torch.int32, "src"); _want(pairs, torch.int32, "pairs")
+    _run("copy_ids", lib().bf_copy_ids, _ptr(dst), _ptr(src), _ptr(pairs), _c_int(n), _stream())
+
+
 # ------------------------------------------------------------------- attention
 def qk_norm_rope_kv_write(qkv: torch.Tensor, q_w: Optional[torch.Tensor],
                           k_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],

@@ -21,8 +21,8 @@ from ..config.registry import load_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .loading import make_env, model_from_dir, model_from_seed
-from .runner import ModelRunner, StepItem
-from .scheduler import FINISHED, Request, Scheduled, Scheduler
+from .runner import ModelRunner, StepError, StepItem
+from .scheduler import FINISHED, PENDING, Request, Scheduled, Scheduler
 
 
 class Engine:
@@ -31,7 +31,7 @@ class Engine:
                  max_kv_memory_gb: float = 10.0, num_pages: Optional[int] = None,
                  page_size: int = 16, max_seq_len: int = 4096, max_batch_size: int = 64,
                  max_tokens_per_step: int = 2048, cuda_graphs: bool = True,
-                 device: str = "cuda:0"):
+                 look_ahead: bool = True, device: str = "cuda:0"):
         """``model``: a folder with config.json and safetensors, or (with
         ``random_seed``) a typed configuration whose weights are drawn on the device."""
         self.env = make_env(dtype, device)
@@ -61,6 +61,8 @@ class Engine:
         self.cuda_graphs = bool(cuda_graphs)
         if self.cuda_graphs:
             self.runner.enable_decode_graphs(max_batch=max_batch_size, max_seq_len=max_seq_len)
+        self.look_ahead = bool(look_ahead)
+        self._pending = None        # (plan, sampling handle, sampled items) of the step in flight
         self._ids = itertools.count()
         self.requests: Dict[Hashable, Request] = {}
         self.tokens_prefilled = 0
@@ -85,36 +87,91 @@ class Engine:
     def abort(self, rid: Hashable) -> None:
         self.scheduler.abort(self.requests[rid])
 
-    def has_work(self) -> bool:
-        return self.scheduler.has_work()
-
     # -------------------------------------------------------------------- step
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._pending is not None
+
+    def _can_look_ahead(self) -> bool:
+        """Whether the next step may be launched before the last one's ids are read: its
+        decode tokens then come from the device.  Not when a token's value is needed on the
+        host first (repetition penalty) or when pages are so short that a request may have
+        to be preempted and recomputed from its tokens."""
+        running = self.scheduler.running
+        if not self.look_ahead or not running:
+            return False
+        if any(r.params.repetition_penalty != 1.0 for r in running):
+            return False
+        return self.runner.cache.can_reserve([(r.rid, r.computed + 1) for r in running
+                                              if r.remaining == 1])
+
+    def _resolve(self, pending) -> List[Request]:
+        """Read back the ids (and the kernels' error word) of a launched step."""
+        plan, handle, sampling = pending
+        ids, err = self.sampler.finish_with_extra(handle) if handle is not None else ([], 0)
+        if err:
+            self.runner.err.zero_()
+            raise StepError(f"a kernel flagged bad input or a timed-out wait (error bits {err})")
+        self.scheduler.resolve(plan, ids)
+        return [s.request for s in sampling]
+
+    def _resolve_pending(self) -> List[Request]:
+        pending, self._pending = self._pending, None
+        return self._resolve(pending)
+
     def step(self) -> List[Request]:
         """One scheduler iteration: plan, run one mixed batch, sample, record.
-        Returns the requests that produced a token in this step."""
+
+        The ids sampled by a step are read back one call later, after the next step has
+        been launched, so that planning and describing a step overlap the previous step's
+        run on the GPU; tokens that a decoding request needs as input travel from the
+        sampler to the next step on the device.  Returns the requests whose token of the
+        previous step has now arrived (with their ``output`` updated)."""
         t0 = time.perf_counter()
+        arrived: List[Request] = []
+        look = self._pending is not None and self._can_look_ahead()
+        if self._pending is not None and not look:
+            arrived = self._resolve_pending()
+        if not self.scheduler.has_work():
+            return arrived
         plan, dropped = self.scheduler.schedule()
         if not plan:
-            return []
-        items = [StepItem(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.sample else [])
-                 for s in plan]
-        logits = self.runner.step(items)
+            if self._pending is not None:
+                arrived += self._resolve_pending()
+            return arrived
+        prev_rows, prev_ids = {}, None
+        if self._pending is not None and self._pending[1] is not None:
+            prev_ids = self._pending[1][0]
+            prev_rows = {id(s.request): i for i, s in enumerate(self._pending[2])}
+        items = []
+        for s in plan:
+            src = None
+            if len(s.tokens) == 1 and s.tokens[0] == PENDING:
+                src = prev_rows[id(s.request)]
+            items.append(StepItem(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.sample else [],
+                                  src_row=src))
+        logits = self.runner.step(items, device_ids=prev_ids)
         sampling = [s for s in plan if s.sample]
-        ids: List[int] = []
+        handle = None
         if sampling:
-            ids = self.sampler.sample(
+            handle = self.sampler.start(
                 logits, [s.request.params for s in sampling],
                 [len(s.request.output) for s in sampling],
-                [s.request.output for s in sampling])
-        self.runner.check_errors()
+                [s.request.output for s in sampling], extra=self.runner.err)
         for s in plan:
             if len(s.tokens) > 1 or not s.request.output:
                 self.tokens_prefilled += len(s.tokens)
             else:
                 self.tokens_decoded += 1
-        self.scheduler.update(plan, ids)
+        self.scheduler.advance(plan)
+        previous, self._pending = self._pending, (plan, handle, sampling)
+        if previous is not None:        # looked ahead: now read the step before this one
+            arrived += self._resolve(previous)
         self.step_ms.append((time.perf_counter() - t0) * 1e3)
-        return [s.request for s in sampling]
+        return arrived
+
+    def flush(self) -> List[Request]:
+        """Read back whatever the last step sampled (nothing else is launched)."""
+        return self._resolve_pending() if self._pending is not None else []
 
     # ---------------------------------------------------------------- generate
     def generate(self, prompts, max_tokens: int = 100, temperature: float = 0.0,
@@ -136,11 +193,23 @@ class Engine:
                 ignore_eos=ignore_eos)
             rids.append(self.add_request(p, params, eos_ids=eos_ids))
         index = {rid: i for i, rid in enumerate(rids)}
-        while any(self.requests[r].state != FINISHED for r in rids):
+        told = {rid: 0 for rid in rids}          # tokens of each request already reported
+
+        def unfinished(r):
+            req = self.requests[r]
+            return req.state != FINISHED or req.unresolved > 0
+
+        while any(unfinished(r) for r in rids):
             for req in self.step():
-                if on_token is not None and req.rid in index:
-                    if on_token(index[req.rid], req.output[-1]) is False:
+                if on_token is None or req.rid not in index:
+                    continue
+                known = [t for t in req.output if t != PENDING]
+                while told[req.rid] < len(known) and req.finish_reason != "abort":
+                    tok = known[told[req.rid]]
+                    told[req.rid] += 1
+                    if on_token(index[req.rid], tok) is False:
                         self.abort(req.rid)
+                        del req.output[told[req.rid]:]
         outs = [self.requests.pop(r).output for r in rids]
         return outs[0] if single else outs
 

@@ -32,6 +32,9 @@ class StepItem:
     rid: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # the (single) token is not known on the host yet: it is row `src_row` of the ids that
+    # the previous step sampled, which are still on the device
+    src_row: Optional[int] = None
 
 
 class StepError(RuntimeError):
@@ -94,7 +97,8 @@ class ModelRunner:
         off, fields = 0, {}
         for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T),
                         ("q_start", B + 1), ("ctx_lens", B), ("state_slots", B),
-                        ("logit_rows", R), ("decode_rows", n_dec), ("prefill_items", 4 * n_pf)):
+                        ("logit_rows", R), ("decode_rows", n_dec), ("prefill_items", 4 * n_pf),
+                        ("id_pairs", 2 * B)):
             fields[name] = (off, n)
             off += n
         for g, w in enumerate(widths):
@@ -106,7 +110,8 @@ class ModelRunner:
 
     def build_context(self, items: Sequence[StepItem], pad_to: Optional[int] = None,
                       widths: Optional[Sequence[int]] = None,
-                      dev: Optional[torch.Tensor] = None) -> StepContext:
+                      dev: Optional[torch.Tensor] = None,
+                      device_ids: Optional[torch.Tensor] = None) -> StepContext:
         """Describe ``items`` to the device.  Pages must already be reserved.
 
         ``pad_to`` (single-token items only) pads the batch with rows that belong to
@@ -142,11 +147,16 @@ class ModelRunner:
 
         tok, pos, sot = view("token_ids"), view("positions"), view("seq_of_token")
         qs, rows = view("q_start"), view("logit_rows")
+        pairs: List[Tuple[int, int]] = []
         t = r = 0
         for b, it in enumerate(items):
             n = q_lens[b]
             if n == 1:
-                tok[t] = it.tokens[0]
+                if it.src_row is not None:
+                    pairs.append((t, it.src_row))
+                    tok[t] = 0
+                else:
+                    tok[t] = it.tokens[0]
                 pos[t] = starts[b]
                 sot[t] = b
             else:
@@ -194,6 +204,8 @@ class ModelRunner:
                     sl[t:t + n] = table[p // ps] * ps + p % ps
                 t += n
 
+        if pairs:
+            view("id_pairs")[:2 * len(pairs)] = np.asarray(pairs, dtype=np.int32).reshape(-1)
         if dev is None:
             dev = torch.empty(total, dtype=torch.int32, device=self.env.device)
         dev[:total].copy_(host[:total], non_blocking=True)
@@ -203,6 +215,12 @@ class ModelRunner:
         def dview(name):
             a, n = fields[name]
             return dev[a:a + n]
+
+        if pairs:
+            if device_ids is None:
+                raise ValueError("an item takes its token from the device, but no ids were given")
+            from ..csrc import ops
+            ops.copy_ids(dview("token_ids"), device_ids, dview("id_pairs"), len(pairs))
 
         return StepContext(
             env=self.env, cache=cache, T=T, B=B,
@@ -231,9 +249,11 @@ class ModelRunner:
         for rid, new_len in wants:
             self.cache.reserve(rid, new_len)
 
-    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem],
+             device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the items as one batch; logits ``[R, vocab]`` float32 on the device, in
-        the order of the items and of each item's ``want``."""
+        the order of the items and of each item's ``want``.  ``device_ids``: int32 ids on
+        the device from which items with ``src_row`` take their token."""
         if not items:
             raise ValueError("a step needs at least one item")
         seen = set()
@@ -248,9 +268,9 @@ class ModelRunner:
             self.cache.zero_fresh_state(self.cache.get(it.rid))
         new_lens = [self.cache.get(it.rid).length + len(it.tokens) for it in items]
         if self._can_replay(items, new_lens):
-            logits = self._graph_step(items)
+            logits = self._graph_step(items, device_ids)
         else:
-            ctx = self.build_context(items)
+            ctx = self.build_context(items, device_ids=device_ids)
             logits = self.model.forward(ctx, self.views)
         for it, new_len in zip(items, new_lens):
             self.cache.commit(it.rid, new_len)
@@ -280,7 +300,8 @@ class ModelRunner:
                 and all(len(it.tokens) == 1 for it in items)
                 and max(new_lens) <= self._graph_seq_len)
 
-    def _graph_step(self, items: Sequence[StepItem]) -> torch.Tensor:
+    def _graph_step(self, items: Sequence[StepItem],
+                    device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         B = len(items)
         bucket = next(b for b in self._buckets if b >= B)
         widths = [-(-self._graph_seq_len // g.page_size) for g in self.cache.groups]
@@ -290,7 +311,8 @@ class ModelRunner:
             st = {"dev": torch.zeros(total, dtype=torch.int32, device=self.env.device),
                   "graph": None, "logits": None}
             self._graphs[bucket] = st
-        ctx = self.build_context(items, pad_to=bucket, widths=widths, dev=st["dev"])
+        ctx = self.build_context(items, pad_to=bucket, widths=widths, dev=st["dev"],
+                                 device_ids=device_ids)
         ctx.max_ctx_len = self._graph_seq_len     # launch shapes must not follow the batch
         if st["graph"] is None:
             logits = self.model.forward(ctx, self.views)      # this step's result, eagerly

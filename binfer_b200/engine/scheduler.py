@@ -38,6 +38,7 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1      # an output token that was sampled on the device and not yet read back
 
 
 @dataclass
@@ -52,6 +53,8 @@ class Request:
     computed: int = 0                        # tokens of `all_tokens` whose keys are cached
     preemptions: int = 0
     order: int = 0                           # admission order among running requests
+    unresolved: int = 0                      # PENDING tokens in `output`
+    drop: int = 0                            # sampled tokens still to come that must be discarded
 
     @property
     def all_tokens(self) -> List[int]:
@@ -228,23 +231,50 @@ class Scheduler:
     def update(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> List[Request]:
         """Record the step: ``sampled`` holds one token per item with ``sample`` set, in
         plan order.  Returns the requests that finished."""
-        done: List[Request] = []
-        it = iter(sampled)
+        self.advance(plan)
+        return self.resolve(plan, sampled)
+
+    def advance(self, plan: Sequence[Scheduled]) -> None:
+        """The step has been launched: cached lengths grow, and every item that samples
+        gets a PENDING output token whose value ``resolve`` fills in later.  What does not
+        depend on the token's value is decided here: the length limits."""
         for s in plan:
             req = s.request
             req.computed += len(s.tokens)
             if not s.sample:
                 continue
-            tok = int(next(it))
-            req.output.append(tok)
+            req.output.append(PENDING)
+            req.unresolved += 1
+            if (len(req.output) >= req.params.max_tokens
+                    or len(req.prompt) + len(req.output) >= self.max_model_len):
+                self._finish(req, "length")
+
+    def resolve(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> List[Request]:
+        """The sampled ids of an advanced step have arrived.  Returns the requests that
+        are finished and have no token outstanding."""
+        done: List[Request] = []
+        it = iter(sampled)
+        for s in plan:
+            if not s.sample:
+                continue
+            req, tok = s.request, int(next(it))
+            if req.drop:                     # sampled after the request had stopped
+                req.drop -= 1
+                continue
+            i = req.output.index(PENDING)
+            req.output[i] = tok
+            req.unresolved -= 1
             stops = () if req.params.ignore_eos else req.eos_ids
-            if tok in stops or tok in req.params.stop_token_ids:
-                self._finish(req, "stop")          # the stop token stays in the output
-            elif len(req.output) >= req.params.max_tokens:
-                self._finish(req, "length")
-            elif len(req.prompt) + len(req.output) >= self.max_model_len:
-                self._finish(req, "length")
-            if req.state == FINISHED:
+            if (tok in stops or tok in req.params.stop_token_ids) and \
+                    req.finish_reason in (None, "length"):
+                # the stop token stays; whatever was sampled after it is discarded
+                req.drop += len(req.output) - (i + 1)
+                req.unresolved -= len(req.output) - (i + 1)
+                del req.output[i + 1:]
+                if req.state != FINISHED:
+                    self._finish(req, "stop")
+                req.finish_reason = "stop"
+            if req.state == FINISHED and req.unresolved == 0:
                 done.append(req)
         return done
 
@@ -257,5 +287,11 @@ class Scheduler:
         req.state, req.finish_reason = FINISHED, reason
 
     def abort(self, req: Request) -> None:
+        """Stop a request now; tokens it still has outstanding are discarded."""
         if req.state != FINISHED:
             self._finish(req, "abort")
+        n = req.output.count(PENDING)
+        if n:
+            req.drop += n
+            req.unresolved -= n
+            req.output[:] = [t for t in req.output if t != PENDING]

@@ -8,7 +8,7 @@ draw run in one kernel per row, and only the chosen ids come back.
 from __future__ import annotations
 
 from collections import Counter
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -32,12 +32,43 @@ class Sampler:
                draw_index: Sequence[int], generated: Sequence[Sequence[int]]) -> List[int]:
         """One token per row of ``logits [R, V]``.  ``draw_index[r]`` is how many tokens
         request r has drawn so far; ``generated[r]`` feeds the repetition penalty."""
+        return self.finish(self.start(logits, params, draw_index, generated))
+
+    def start(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+              draw_index: Sequence[int], generated: Sequence[Sequence[int]],
+              extra: Optional[torch.Tensor] = None):
+        """Launch the sampling and the copy of the ids to pinned host memory; returns a
+        handle ``(device ids, host ids, event)`` for :meth:`finish`.  ``extra``: one int32
+        word on the device (the kernels' error word) that rides back with the ids."""
         R = logits.shape[0]
         assert R == len(params) == len(draw_index) == len(generated)
         out = self.sample_async(logits, params, draw_index, generated)
-        ids = out.cpu()
-        self.d2h_bytes += R * 4
-        return ids.tolist()
+        self._id_turn = (getattr(self, "_id_turn", 0) + 1) % 4
+        bufs = self.__dict__.setdefault("_id_bufs", [None] * 4)
+        host = bufs[self._id_turn]
+        if host is None or host.numel() < R + 1:
+            host = bufs[self._id_turn] = torch.empty(max(R, 64) + 1, dtype=torch.int32,
+                                                     pin_memory=True)
+        host[:R].copy_(out, non_blocking=True)
+        if extra is not None:
+            host[R:R + 1].copy_(extra, non_blocking=True)
+        else:
+            host[R] = 0
+        ev = torch.cuda.Event()
+        ev.record()
+        self.d2h_bytes += R * 4 + (4 if extra is not None else 0)
+        return out, host[:R + 1], ev
+
+    def finish(self, handle) -> List[int]:
+        """Wait for a started sampling and return its ids."""
+        return self.finish_with_extra(handle)[0]
+
+    def finish_with_extra(self, handle):
+        """(ids, the extra word) of a started sampling."""
+        _, host, ev = handle
+        ev.synchronize()
+        vals = host.tolist()
+        return vals[:-1], vals[-1]
 
     def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                      draw_index: Sequence[int], generated: Sequence[Sequence[int]]) -> torch.Tensor:

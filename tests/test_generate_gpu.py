@@ -112,3 +112,29 @@ def test_cli_generates(cuda_device, tmp_path, capsys):
                "fp32", "--ignore-eos", "-q", "--kv-pages", "32"])
     assert rc == 0
     assert capsys.readouterr().out.split() == [str(t) for t in want]
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_look_ahead_gives_the_same_tokens(cuda_device, tmp_path, temperature):
+    """Launching a step before the last one's ids are read changes nothing: same tokens
+    as the synchronous loop, stop tokens honoured, nothing sampled after them kept."""
+    d = H.make_model_dir(tmp_path, "B")
+    raw, w = H.read_model_dir(d)
+    prompts = [H.random_tokens(n, raw["vocab_size"], 3 * n) for n in (4, 31, 9, 17)]
+    kw = dict(max_tokens=24, temperature=temperature, seed=11, ignore_eos=True)
+    sync = _engine(d, page_size=8, look_ahead=False)
+    want = sync.generate(prompts, **kw)
+    ahead = _engine(d, page_size=8, look_ahead=True)
+    assert ahead.generate(prompts, **kw) == want
+    # a stop token in the middle of a request's output
+    stop = want[1][7]
+    cut = [o[:o.index(stop) + 1] if stop in o else o for o in want]
+    kw2 = dict(kw, ignore_eos=False, eos_ids=[stop])
+    assert _engine(d, page_size=8, look_ahead=False).generate(prompts, **kw2) == cut
+    eng = _engine(d, page_size=8, look_ahead=True)
+    assert eng.generate(prompts, **kw2) == cut
+    assert eng.stats()["pages_free"] == eng.stats()["pages_total"] and not eng.has_work()
+    # few pages: preemption switches the look-ahead off where it must, tokens stay the same
+    tight = _engine(d, page_size=8, num_pages=14, look_ahead=True)
+    assert tight.generate(prompts, **kw) == want
+    assert tight.stats()["preemptions"] > 0
