@@ -57,7 +57,7 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while running."""
+    """nvidia-smi clocks and throttle reasons, sampled every 100 ms while running."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -70,7 +70,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -159,7 +159,7 @@ def time_decode(runner, sampler, rids, vocab, steps, warmup, gen, clocks=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
@@ -233,12 +233,19 @@ def main():
         return 0
 
     # ---- end to end through the entry point: scheduler, H2D inputs, D2H ids every step
-    prompts = [torch.randint(0, vocab, (CONTEXT - (steps + warmup) - 1,), generator=gen).tolist()
-               for _ in range(B)]
+    # (the clock sampler is stopped first: its nvidia-smi queries contend with the host's
+    # CUDA calls, which this measurement, unlike the device-timed one, has in its loop)
+    clocks.stop()
+    # prompts are prefilled in portions, so the requests start decoding a few steps apart;
+    # they are given room enough that none finishes (and the batch does not shrink) while
+    # the steps are timed
+    slack = 2 * B + 8
+    prompts = [torch.randint(0, vocab, (CONTEXT - (steps + warmup) - slack,),
+                             generator=gen).tolist() for _ in range(B)]
     from binfer_b200.sampling import SamplingParams
     for p in prompts:
-        engine.add_request(p, SamplingParams(max_tokens=steps + warmup + 1, ignore_eos=True,
-                                             seed=0))
+        engine.add_request(p, SamplingParams(max_tokens=steps + warmup + slack - 1,
+                                             ignore_eos=True, seed=0))
     while any(r.remaining > 1 or not r.output for r in engine.scheduler.running) \
             or engine.scheduler.waiting:
         engine.step()                                   # prefill portions
@@ -285,7 +292,6 @@ def main():
             + 2 * H * vocab
         prefill = {"value": T / (pf_ms / 1e3), "tokens": T, "ms": pf_ms,
                    "frac": flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
-    clocks.stop()
     runner.check_errors()
 
     out = {
@@ -301,6 +307,7 @@ def main():
             "vocab": cfg.vocab_size, "tied": cfg.tie_word_embeddings, "global_batch": B,
             "seq_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "1 GPU",
             "cuda_graphs": not args.eager, "l2": "inputs larger than L2 (weights 15 GB per step)",
+            "clocks_sampled": "during the device-timed steps",
             "peaks": peaks["source"],
         },
         "clocks": clk,
