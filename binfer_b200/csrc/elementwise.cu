@@ -212,10 +212,42 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
   }
 }
 
+// bf16, I a multiple of 8: eight elements per thread with 16-byte loads and stores.
+__global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
+                                         __nv_bfloat16* __restrict__ out, int T, int I) {
+  const int per_row = I / 8;
+  const size_t n = (size_t)T * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    const size_t t = i / per_row, c = (i - t * per_row) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      o2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * I + c) = o4;
+  }
+}
+
 BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype,
                           cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = 256;
+  if (act_dtype == BF_DTYPE_BF16 && I % 8 == 0 && ((uintptr_t)gu & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0) {
+    long long blocks = ((long long)T * (I / 8) + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    silu_mul_bf16_vec_kernel<<<(int)blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
+    return bf_launch_status();
+  }
   long long blocks = ((long long)T * I + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (act_dtype == BF_DTYPE_F32)

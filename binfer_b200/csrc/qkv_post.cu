@@ -77,6 +77,79 @@ __global__ void qk_norm_rope_kv_write_kernel(
   for (int i = lane; i < d; i += 32) bf_st(dst + i, x[i]);
 }
 
+// The common case in registers: bf16, head size 128, full rotation (64 pairs).  A block per
+// token: the 64 sines and cosines of the token's position are computed once and shared by
+// all its heads; each warp then walks heads, lane l holding elements 4l..4l+3, whose
+// rotation partners sit in lane l ^ 16.
+__global__ void qk_norm_rope_kv_write_d128_kernel(
+    const __nv_bfloat16* __restrict__ qkv, long long row_stride, const float* __restrict__ q_w,
+    const float* __restrict__ k_w, const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, const int* __restrict__ slots,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+    __nv_bfloat16* __restrict__ v_cache, int nh, int nkv, int page_size, long long num_slots,
+    float eps, int* __restrict__ err) {
+  constexpr int D = 128;
+  __shared__ float sn_s[64], cs_s[64];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x;
+  if (threadIdx.x < 64) {
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[threadIdx.x], &sn, &cs);
+    sn_s[threadIdx.x] = sn;
+    cs_s[threadIdx.x] = cs;
+  }
+  __syncthreads();
+  const int slot = k_cache ? slots[t] : -1;
+  const bool upper = lane >= 16;               // holds elements i + 64 of the pairs
+  const int fi = (lane & 15) * 4;
+  const float4 wq = q_w ? *reinterpret_cast<const float4*>(q_w + lane * 4) : make_float4(1, 1, 1, 1);
+  const float4 wk = k_w ? *reinterpret_cast<const float4*>(k_w + lane * 4) : make_float4(1, 1, 1, 1);
+  for (int hh = warp; hh < nh + 2 * nkv; hh += warps) {
+    const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+    if (!is_q && slot < 0) continue;
+    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride +
+                                                      (size_t)hh * D + lane * 4);
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(r2[0]), b = __bfloat1622float2(r2[1]);
+    float x[4] = {a.x, a.y, b.x, b.y};
+    if (is_q || is_k) {
+      if (is_q ? q_w != nullptr : k_w != nullptr) {
+        const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        const float4 w4 = is_q ? wq : wk;
+        x[0] *= inv * w4.x;
+        x[1] *= inv * w4.y;
+        x[2] *= inv * w4.z;
+        x[3] *= inv * w4.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+        const float sn = sn_s[fi + j], cs = cs_s[fi + j];
+        // lower half: x[i] cos - x[i+64] sin;  upper half: x[i] sin + x[i+64] cos
+        x[j] = upper ? other * sn + x[j] * cs : x[j] * cs - other * sn;
+      }
+    }
+    uint2 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+    o2[0] = __floats2bfloat162_rn(x[0], x[1]);
+    o2[1] = __floats2bfloat162_rn(x[2], x[3]);
+    if (is_q) {
+      *reinterpret_cast<uint2*>(q_out + ((size_t)t * nh + hh) * D + lane * 4) = o;
+      continue;
+    }
+    if ((long long)slot >= num_slots) {
+      if (lane == 0) atomicOr(err, BF_ERR_SLOT);
+      continue;
+    }
+    const int h = is_k ? hh - nh : hh - nh - nkv;
+    const int page = slot / page_size, off = slot - page * page_size;
+    __nv_bfloat16* dst =
+        (is_k ? k_cache : v_cache) + (((size_t)page * nkv + h) * page_size + off) * D;
+    *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+  }
+}
+
 BF_EXPORT int bf_qk_norm_rope_kv_write(
     const void* qkv, long long row_stride, const float* q_w, const float* k_w,
     const float* inv_freq, int rot_half, const int* positions, const int* slots, void* q_out,
@@ -87,6 +160,16 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
   const int warps = 4;
   const int total = nh + 2 * nkv;
   dim3 grid(T, (total + warps - 1) / warps);
+  if (act_dtype == BF_DTYPE_BF16 && d == 128 && rot_half == 64 && row_stride % 4 == 0 &&
+      ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_cache & 7) == 0 &&
+      ((uintptr_t)v_cache & 7) == 0 && ((uintptr_t)inv_freq & 15) == 0 &&
+      ((uintptr_t)q_w & 15) == 0 && ((uintptr_t)k_w & 15) == 0) {
+    qk_norm_rope_kv_write_d128_kernel<<<T, total >= 16 ? 256 : 128, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, row_stride, q_w, k_w, inv_freq, positions, slots,
+        (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv,
+        page_size, num_slots, eps, err);
+    return bf_launch_status();
+  }
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   if (act_dtype == BF_DTYPE_F32)

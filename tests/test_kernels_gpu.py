@@ -94,7 +94,8 @@ def test_sgemm_true_float32(cuda_device, M):
 # ------------------------------------------------------- q/k norm, rotation, cache write
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("nh,nkv,d,rot,norm", [(3, 1, 16, 16, True), (4, 2, 48, 24, True),
-                                               (2, 2, 128, 128, False), (5, 5, 80, 0, True)])
+                                               (2, 2, 128, 128, False), (5, 5, 80, 0, True),
+                                               (8, 2, 128, 128, True), (3, 1, 128, 64, True)])
 def test_qk_norm_rope_kv_write(cuda_device, dtype, nh, nkv, d, rot, norm):
     from binfer_b200.csrc import ops
     T, ps, pages, eps, theta = 11, 4, 9, 1e-5, 5000.0
@@ -364,12 +365,12 @@ def test_engine_with_own_gemm_everywhere(cuda_device, tmp_path):
 @pytest.mark.parametrize("nh,nkv,d,ps,window,spike", [
     (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
     (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 70, True), (2, 1, 256, 16, 100, True),
-    (4, 4, 128, 64, 130, True)])
+    (4, 4, 128, 64, 130, True), (6, 2, 128, 8, None, True), (4, 1, 64, 32, 150, True)])
 def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike):
     """Portions that start in the middle of a prompt, straddle 64-key tiles and pages, next to
     whole prompts; the far key and the window's edge are made to stand out."""
     from binfer_b200.csrc import ops
-    ctxs, qlens = [70, 200, 129, 300, 64, 2], [70, 37, 5, 130, 64, 2]
+    ctxs, qlens = [70, 200, 129, 300, 64, 2, 400], [70, 37, 5, 130, 64, 2, 290]
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
                                                    qlens, window, spike, seed=11)
     items, row = [], 0
