@@ -41,7 +41,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q,
 
   const int* it = items + 4 * blockIdx.z;
   const int seq = it[0], row0 = it[1], qlen = it[2], pos0 = it[3];
-  const int qt = blockIdx.x, h = blockIdx.y;
+  // the last query tiles see the most keys: they are launched first
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
   if (qt * PF_BM >= qlen) return;
   const int g = h / (nh / nkv);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

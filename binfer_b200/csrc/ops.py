@@ -232,16 +232,34 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       items: torch.Tensor, n_items: int, max_rows: int,
                       block_tables: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, d: int,
-                      window: Optional[int], scale: float, err: torch.Tensor) -> None:
+                      window: Optional[int], scale: float, err: torch.Tensor,
+                      variant: str = "auto") -> None:
     """Causal flash attention over the pages for prompt portions (bfloat16 only).
-    ``items`` int32 [n, 4]: (request index, first token row, rows, first position)."""
+    ``items`` int32 [n, 4]: (request index, first token row, rows, first position).
+    ``variant``: ``umma`` (tcgen05 tensor cores, TMA loads; head sizes 64/128, page sizes
+    8..64 that divide 64), ``mma_sync`` (every size in DECODE_HEAD_DIMS, any page size), or
+    ``auto``: umma where it applies."""
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"prefill_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
     _want(items, torch.int32, "items")
+    page_size = k_cache.shape[2]
+    umma_ok = (d in (64, 128) and 8 <= page_size <= 64 and 64 % page_size == 0
+               and q.is_contiguous() and q.data_ptr() % 16 == 0)
+    if variant == "umma" and not umma_ok:
+        raise KernelError(f"prefill_attention: the umma variant does not take head_dim {d} with "
+                          f"pages of {page_size}")
+    if umma_ok and variant != "mma_sync":
+        _run("prefill_attention_umma", lib().bf_prefill_attention_umma,
+             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
+             _c_int(max_rows), _c_int(q.shape[0]), _ptr(block_tables),
+             _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv), _c_int(d),
+             _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0), _c_float(scale),
+             _ptr(err), _stream())
+        return
     _run("prefill_attention", lib().bf_prefill_attention,
          _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items), _c_int(max_rows),
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv),
-         _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]), _c_int(window or 0),
+         _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
          _c_float(scale), _ptr(err), _stream())
 
 

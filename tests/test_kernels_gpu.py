@@ -366,10 +366,13 @@ def test_engine_with_own_gemm_everywhere(cuda_device, tmp_path):
     (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
     (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 70, True), (2, 1, 256, 16, 100, True),
     (4, 4, 128, 64, 130, True), (6, 2, 128, 8, None, True), (4, 1, 64, 32, 150, True)])
-def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike):
+@pytest.mark.parametrize("variant", ["mma_sync", "umma"])
+def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike, variant):
     """Portions that start in the middle of a prompt, straddle 64-key tiles and pages, next to
     whole prompts; the far key and the window's edge are made to stand out."""
     from binfer_b200.csrc import ops
+    if variant == "umma" and not (d in (64, 128) and ps >= 8 and 64 % ps == 0):
+        pytest.skip("the umma variant does not take this head or page size")
     ctxs, qlens = [70, 200, 129, 300, 64, 2, 400], [70, 37, 5, 130, 64, 2, 290]
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
                                                    qlens, window, spike, seed=11)
@@ -381,13 +384,13 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
     out = torch.zeros_like(q)
     err = _err(cuda_device)
     ops.prefill_attention(q, kc, vc, items, len(ctxs), max(qlens), bt, out, nh, nkv, d, window,
-                          d ** -0.5, err)
+                          d ** -0.5, err, variant=variant)
     assert int(err.item()) == 0
     _close(out, ref, BF16)
     # a subset of the portions leaves the other rows alone
     out2 = torch.zeros_like(q)
     ops.prefill_attention(q, kc, vc, items[1:3].contiguous(), 2, 37, bt, out2, nh, nkv, d,
-                          window, d ** -0.5, err)
+                          window, d ** -0.5, err, variant=variant)
     assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
 
 
