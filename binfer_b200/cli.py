@@ -233,7 +233,7 @@ def main(argv: Optional[List[str]] = None) -> int:
               num_pages=args["kv_pages"], page_size=args["page_size"],
               max_seq_len=args["max_seq_len"], max_batch_size=args["max_batch_size"],
               max_tokens_per_step=args["max_tokens_per_step"],
-              cuda_graphs=args["cuda_graphs"] and not args["profile"])
+              cuda_graphs=args["cuda_graphs"] and not args["profile"] and not args["trace"])
     try:
         if args["random_weights"] is not None:
             engine = Engine(load_config(model), random_seed=args["random_weights"], **kw)
@@ -290,6 +290,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             log(f"[{len(out)} tokens, {dt:.2f}s, {len(out) / dt:.1f} tok/s]")
     except CliError as e:
         print(e, file=sys.stderr)
+        return 1
+    except (ValueError, RuntimeError) as e:
+        print(f"Error: {e}", file=sys.stderr)
         return 1
     if prof is not None:
         if args["profile"]:
