@@ -30,7 +30,16 @@ TINY_W = dict(
     layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
     max_position_embeddings=2048, hidden_act="silu", attention_bias=False)
 
+# head size 128 and pages of 16: the sizes the TMA / tcgen05 kernels are written for
+TINY_M = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=256,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
+    vocab_size=500, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
+    attention_bias=False)
+
 TINY = {
+    "M": dict(raw=TINY_M, std=0.05, norm_std=0.02, page_size=16, seed=44),
     "A": dict(raw=TINY_A, std=0.02, norm_std=0.01, page_size=16, seed=11),
     "B": dict(raw=TINY_B, std=0.05, norm_std=0.05, page_size=8, seed=22),
     "W": dict(raw=TINY_W, std=0.04, norm_std=0.03, page_size=4, seed=33),

@@ -17,7 +17,8 @@ TOL = {torch.float32: 2e-5, torch.bfloat16: 3e-2}
 # and root-mean-square of the difference over that of the reference
 TOL_RMS = {torch.float32: 5e-6, torch.bfloat16: 1e-2}
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 70], "W": [3, 30, 64, 101]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 70], "W": [3, 30, 64, 101],
+           "M": [2, 45, 150, 333]}
 
 
 def _requests(which, extra=()):
@@ -69,7 +70,7 @@ def _compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["A", "B", "W"])
+@pytest.mark.parametrize("which", ["A", "B", "W", "M"])
 @pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
 def test_replay(cuda_device, plain_logits, which, dtype, regime):
     extra = (55, 61) if regime == "mixed" else ()
@@ -86,7 +87,7 @@ def test_replay(cuda_device, plain_logits, which, dtype, regime):
     _compare(got, ref, dtype, f"{which}/{regime}")
 
 
-@pytest.mark.parametrize("which", ["A", "B", "W"])
+@pytest.mark.parametrize("which", ["A", "B", "W", "M"])
 def test_regimes_agree_bitwise_in_float32(cuda_device, plain_logits, which):
     """In float32 the order of every sum is fixed by the position alone, so cutting
     and batching change nothing at all."""
@@ -123,3 +124,20 @@ def test_first_tokens(cuda_device, plain_logits):
         steps = H.trace_decode_tail(reqs, tail=5)
         runner = _runner(model_dir, torch.float32, H.TINY[which]["page_size"], 4)
         _compare(H.run_trace(runner, steps), ref, torch.float32, f"{which}/first tokens")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_replay_through_captured_decode_steps(cuda_device, plain_logits, dtype):
+    """Steps of single tokens replayed from CUDA graphs (padded to a bucket, block tables of
+    full width) give what eager steps give."""
+    which = "M"
+    reqs = _requests(which, (55, 61))
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    ps = H.TINY[which]["page_size"]
+    for make in (H.trace_decode_tail, H.trace_mixed):
+        steps = make(reqs)
+        runner = _runner(model_dir, dtype, ps, H.peak_pages(steps, ps))
+        runner.enable_decode_graphs(max_batch=8, max_seq_len=512)
+        got = H.run_trace(runner, steps)
+        assert getattr(runner, "graph_replays", 0) > 0
+        _compare(got, ref, dtype, f"{which}/graphs/{make.__name__}")
