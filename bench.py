@@ -43,7 +43,7 @@ QWEN3_8B = dict(
     attention_bias=False, use_sliding_window=False)
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
-PAGE_SIZE = 16
+PAGE_SIZE = 64
 
 
 def load_peaks():

@@ -63,7 +63,7 @@ Options:
   --random-weights <seed>  Draw random weights for the folder's config.json (no safetensors needed)
   --kv-memory-gb <f>       Memory for the key/value cache (default: 10)
   --kv-pages <n>           Size of the cache in pages instead
-  --page-size <n>          Tokens per cache page (default: 16)
+  --page-size <n>          Tokens per cache page (default: 64)
   --max-tokens-per-step <n>  Token budget of one step (default: 2048)
   --max-seq-len <n>        Longest sequence (default: 4096)
   --max-batch-size <n>     Most requests running at once (default: 64)
@@ -111,7 +111,7 @@ def parse_args(argv: List[str]) -> dict:
              bench=False, profile=False, trace=None, quiet=False, verbose=False, cuda_graphs=True,
              temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=None,
              ignore_eos=False, input=None, output=None, use_template=False, random_weights=None,
-             kv_memory_gb=10.0, kv_pages=None, page_size=16, max_tokens_per_step=2048,
+             kv_memory_gb=10.0, kv_pages=None, page_size=64, max_tokens_per_step=2048,
              max_seq_len=4096, max_batch_size=64)
     names = {"--max-tokens": ("max_tokens", int), "--tp": ("tp", str), "--dtype": ("dtype", str),
              "-p": ("prompt", str), "--prompt": ("prompt", str), "--prompt-ids": ("prompt", str),

@@ -241,6 +241,8 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ part_o,
                                               int max_splits) {
   __shared__ float wgt[MERGE_CHUNK];
   __shared__ float sh_M, sh_L;
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int r = blockIdx.x, h = blockIdx.y;
   const int t = rows ? rows[r] : r;
   const int p = positions[t];
@@ -366,9 +368,9 @@ BF_EXPORT int bf_decode_attention_merge(const float* part_o, const float* part_m
   if (n_rows <= 0) return 0;
 #define BF_MERGE_CASE(DD)                                                                  \
   case DD:                                                                                 \
-    decode_attention_merge_kernel<DD><<<dim3(n_rows, nh), 128, 0, stream>>>(               \
-        part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);    \
-    return bf_launch_status()
+    return bf_launch_pdl(decode_attention_merge_kernel<DD>, dim3(n_rows, nh), dim3(128), 0,  \
+                         stream, part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh,  \
+                         window, max_splits)
   switch (d) {
     BF_MERGE_CASE(32);
     BF_MERGE_CASE(64);

@@ -53,6 +53,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + HALVES * HALF_ELEMS);   // [2]: K, V
   float* red_far = reinterpret_cast<float*>(bars + 2);                      // merge buffer if G > 16
 
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
   const int t = rows ? rows[r] : r;
   const int p = positions[t];
@@ -285,11 +287,10 @@ static int launch_tma(const void* q, const void* k_cache, const void* v_cache, c
     configured = true;
   }
   dim3 grid(max_splits, nkv, n_rows);
-  kern<<<grid, DT_THREADS, smem, stream>>>(
-      mk, mv, (const __nv_bfloat16*)q, rows, seq_of_token, positions, block_tables, table_stride,
-      part_o, part_ml, nh, nkv, page_size, num_pages, window, max_splits,
-      scale * 1.4426950408889634f, err);
-  return bf_launch_status();
+  return bf_launch_pdl(kern, grid, dim3(DT_THREADS), smem, stream, mk, mv,
+                       (const __nv_bfloat16*)q, rows, seq_of_token, positions, block_tables,
+                       table_stride, part_o, part_ml, nh, nkv, page_size, num_pages, window,
+                       max_splits, scale * 1.4426950408889634f, err);
 }
 
 // Same arguments and result as bf_decode_attention.  Returns cudaErrorInvalidValue for head

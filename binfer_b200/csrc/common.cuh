@@ -55,3 +55,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int bf_launch_status() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------- programmatic dependent launch
+// A kernel launched through bf_launch_pdl may be scheduled while its predecessor on the
+// stream is still running (its blocks become resident, its prologue runs), which hides the
+// launch latency between the short kernels of a decode step.  Such a kernel must call
+// bf_pdl_wait() before it touches global memory: the call returns when every earlier grid
+// has completed and its writes are visible.  bf_pdl_trigger() lets the kernel after this one
+// be scheduled early in turn.  Launched the ordinary way, both calls do nothing.
+__device__ __forceinline__ void bf_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void bf_pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+int bf_pdl_enabled();    // defined in elementwise.cu; switched by bf_set_pdl()
+
+template <typename... KArgs, typename... Args>
+static inline int bf_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = bf_pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return bf_launch_status();
+}

@@ -5,7 +5,21 @@
 // activation type.  The reference rounds the stream to bf16 after every add
 // (cuda/kernels/bf16_kernels.cu:504-517) and runs norm and add as separate
 // kernels (src/engine/batched_engine.ts:1164-1178).
+#include <stdlib.h>
+
 #include "common.cuh"
+
+static int g_pdl = -1;
+int bf_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("BINFER_B200_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+// 1: launch the decode step's short kernels with programmatic dependent launch (default);
+// 0: ordinary launches.  The environment variable BINFER_B200_PDL=0 does the same.
+BF_EXPORT void bf_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 // ------------------------------------------------------------------ embedding
 // out[t, :] = table[ids[t], :] * scale   (cuda/kernels/bf16_kernels.cu:711-729,
@@ -14,6 +28,8 @@ template <typename W>
 __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int vocab, float scale,
                                     int* __restrict__ err) {
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * H;
@@ -32,12 +48,10 @@ BF_EXPORT int bf_embed_gather(const void* table, int table_dtype, const int* ids
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == BF_DTYPE_F32)
-    embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H,
-                                                          vocab, scale, err);
-  else
-    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
-        (const __nv_bfloat16*)table, ids, out, H, vocab, scale, err);
-  return bf_launch_status();
+    return bf_launch_pdl(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream,
+                         (const float*)table, ids, out, H, vocab, scale, err);
+  return bf_launch_pdl(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+                       (const __nv_bfloat16*)table, ids, out, H, vocab, scale, err);
 }
 
 // -------------------------------------------------------- add + RMSNorm (fused)
@@ -81,6 +95,8 @@ __global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid,
                                             const int* __restrict__ rows, int H, float eps,
                                             int write_back) {
   __shared__ float scratch[33];
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * H;
@@ -142,14 +158,14 @@ BF_EXPORT int bf_add_rmsnorm(float* resid, const void* delta, const float* w, vo
       ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const int threads = H >= 2048 ? 256 : 128;
     const int trips = (H / 8 + threads - 1) / threads;
-    auto args = [&](auto kern) {
-      kern<<<n_rows, threads, 0, stream>>>(resid, (const __nv_bfloat16*)delta, w,
-                                           (__nv_bfloat16*)out, rows, H, eps, write_back);
+    auto go = [&](auto kern) {
+      return bf_launch_pdl(kern, dim3(n_rows), dim3(threads), 0, stream, resid,
+                           (const __nv_bfloat16*)delta, w, (__nv_bfloat16*)out, rows, H, eps,
+                           write_back);
     };
-    if (trips <= 1) args(add_rmsnorm_bf16_vec_kernel<1>);
-    else if (trips == 2) args(add_rmsnorm_bf16_vec_kernel<2>);
-    else args(add_rmsnorm_bf16_vec_kernel<4>);
-    return bf_launch_status();
+    if (trips <= 1) return go(add_rmsnorm_bf16_vec_kernel<1>);
+    if (trips == 2) return go(add_rmsnorm_bf16_vec_kernel<2>);
+    return go(add_rmsnorm_bf16_vec_kernel<4>);
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const size_t smem = (size_t)(H + 33) * sizeof(float);
@@ -215,6 +231,8 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
 // bf16, I a multiple of 8: eight elements per thread with 16-byte loads and stores.
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
                                          __nv_bfloat16* __restrict__ out, int T, int I) {
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int per_row = I / 8;
   const size_t n = (size_t)T * per_row;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -244,9 +262,8 @@ BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype
       ((uintptr_t)out & 15) == 0) {
     long long blocks = ((long long)T * (I / 8) + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    silu_mul_bf16_vec_kernel<<<(int)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
-    return bf_launch_status();
+    return bf_launch_pdl(silu_mul_bf16_vec_kernel, dim3((int)blocks), dim3(threads), 0, stream,
+                         (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
   }
   long long blocks = ((long long)T * I + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
@@ -264,6 +281,8 @@ BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype
 // input tokens without a trip through the host.
 __global__ void copy_ids_kernel(int* __restrict__ dst, const int* __restrict__ src,
                                 const int* __restrict__ pairs, int n) {
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[pairs[2 * i]] = src[pairs[2 * i + 1]];
 }

@@ -71,6 +71,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                     const ClusterGemmParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf_pdl_trigger();
   uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(base);
   uint64_t* empty = full + CL_MAX_STAGES;
@@ -114,6 +115,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers and tensor memory are set up; only now does the kernel need its inputs
+  bf_pdl_wait();
 
   if (warp == 2) {
     if (lane == 0) {
@@ -243,13 +246,15 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   cfg.blockDim = dim3(96, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = p.cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = bf_pdl_enabled();
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, mx, mw, out, p);
   if (ce != cudaSuccess) return (int)ce;
   return bf_launch_status();

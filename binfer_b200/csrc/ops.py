@@ -204,22 +204,35 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
     ``rows`` lists the token rows to run (None: rows 0..n_rows-1); ``max_ctx_len``
     bounds the context of every such row.  Scratch for the splits' partial results
-    is taken from torch's allocator.  ``variant``: ``tma`` (bulk tensor copies; head
-    sizes 64/128/256, page sizes 8..128 that divide 128), ``cp_async`` (every size in
-    DECODE_HEAD_DIMS, any page size), or ``auto``: tma where it applies."""
+    is taken from torch's allocator.  ``variant``: ``persistent`` (resident CTAs that walk
+    the work with a ring of TMA-fed tiles; head sizes 64/128/256, page sizes 8..128 that
+    divide 128, at most 16 query heads per kv head and 512 rows), ``tma`` (one CTA per split,
+    bulk tensor copies; the same head and page sizes), ``cp_async`` (every size in
+    DECODE_HEAD_DIMS, any page size), or ``auto``: the first of these that applies."""
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"decode_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
+    if variant not in ("auto", "persistent", "tma", "cp_async"):
+        raise KernelError(f"decode_attention: unknown variant {variant!r}")
     page_size = k_cache.shape[2]
     tma_ok = d in (64, 128, 256) and 8 <= page_size <= 128 and 128 % page_size == 0
+    persistent_ok = (tma_ok and nh // nkv <= 16 and n_rows <= 512 and q.is_contiguous()
+                     and q.data_ptr() % 16 == 0)
     if variant == "tma" and not tma_ok:
         raise KernelError(f"decode_attention: the tma variant does not take head_dim {d} with "
                           f"pages of {page_size}")
-    use_tma = tma_ok and variant != "cp_async"
+    if variant == "persistent" and not persistent_ok:
+        raise KernelError(f"decode_attention: the persistent variant does not take head_dim {d}, "
+                          f"pages of {page_size}, {nh // nkv} heads per kv head, {n_rows} rows")
+    if persistent_ok and variant in ("auto", "persistent"):
+        name, fn = "decode_attention_persistent", lib().bf_decode_attention_persistent
+    elif tma_ok and variant != "cp_async":
+        name, fn = "decode_attention_tma", lib().bf_decode_attention_tma
+    else:
+        name, fn = "decode_attention", lib().bf_decode_attention
     max_splits = max(1, -(-int(max_ctx_len) // DECODE_SPLIT_KEYS))
     part_o = torch.empty((n_rows, nh, max_splits, d), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_rows, nh, max_splits, 2), dtype=torch.float32, device=q.device)
-    fn = lib().bf_decode_attention_tma if use_tma else lib().bf_decode_attention
-    _run("decode_attention_tma" if use_tma else "decode_attention", fn,
+    _run(name, fn,
          _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(rows), _ptr(seq_of_token), _ptr(positions),
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _ptr(part_o),
          _ptr(part_ml), _c_int(n_rows), _c_int(nh), _c_int(nkv), _c_int(d),

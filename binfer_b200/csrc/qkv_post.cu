@@ -90,6 +90,8 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
     float eps, int* __restrict__ err) {
   constexpr int D = 128;
   __shared__ float sn_s[64], cs_s[64];
+  bf_pdl_wait();
+  bf_pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x;
   if (threadIdx.x < 64) {
@@ -164,11 +166,11 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
       ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_cache & 7) == 0 &&
       ((uintptr_t)v_cache & 7) == 0 && ((uintptr_t)inv_freq & 15) == 0 &&
       ((uintptr_t)q_w & 15) == 0 && ((uintptr_t)k_w & 15) == 0) {
-    qk_norm_rope_kv_write_d128_kernel<<<T, total >= 16 ? 256 : 128, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, row_stride, q_w, k_w, inv_freq, positions, slots,
-        (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv,
-        page_size, num_slots, eps, err);
-    return bf_launch_status();
+    return bf_launch_pdl(qk_norm_rope_kv_write_d128_kernel, dim3(T),
+                         dim3(total >= 16 ? 256 : 128), 0, stream, (const __nv_bfloat16*)qkv,
+                         row_stride, q_w, k_w, inv_freq, positions, slots, (__nv_bfloat16*)q_out,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, page_size,
+                         num_slots, eps, err);
   }
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;

@@ -29,7 +29,7 @@ class Engine:
     def __init__(self, model: Union[str, object], dtype: str = "bfloat16", *,
                  random_seed: Optional[int] = None, random_std: float = 0.02,
                  max_kv_memory_gb: float = 10.0, num_pages: Optional[int] = None,
-                 page_size: int = 16, max_seq_len: int = 4096, max_batch_size: int = 64,
+                 page_size: int = 64, max_seq_len: int = 4096, max_batch_size: int = 64,
                  max_tokens_per_step: int = 2048, cuda_graphs: bool = True,
                  look_ahead: bool = True, device: str = "cuda:0"):
         """``model``: a folder with config.json and safetensors, or (with

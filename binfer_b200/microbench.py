@@ -179,7 +179,7 @@ def main(argv=None):
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--features", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -188,7 +188,7 @@ def main(argv=None):
     ap.add_argument("--cluster", type=int, default=0,
                     help="gemm: split K over clusters of this many CTAs (needs --bn)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host, no CUDA graph")
-    ap.add_argument("--variant", default="auto", choices=["auto", "tma", "cp_async", "umma", "mma_sync"],
+    ap.add_argument("--variant", default="auto", choices=["auto", "persistent", "tma", "cp_async", "umma", "mma_sync"],
                     help="decode attention: tma or cp_async tile loads; prefill attention: "
                          "umma (tcgen05) or mma_sync")
     a = ap.parse_args(argv)

@@ -214,13 +214,15 @@ def test_paged_attention_generic(cuda_device, dtype, nh, nkv, d, ps, window, spi
     (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
     (32, 8, 128, 16, None, False), (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 200, True),
     (2, 1, 256, 16, 100, True), (20, 1, 64, 16, None, True), (4, 4, 128, 64, 130, True)])
-@pytest.mark.parametrize("variant", ["cp_async", "tma"])
+@pytest.mark.parametrize("variant", ["cp_async", "tma", "persistent"])
 def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike, variant):
-    """Contexts on both sides of the 128-key split edge, and long ones; both ways of
+    """Contexts on both sides of the 128-key split edge, and long ones; every way of
     fetching the tiles."""
     from binfer_b200.csrc import ops
-    if variant == "tma" and not (d in (64, 128, 256) and ps >= 8 and 128 % ps == 0):
-        pytest.skip("the tma variant does not take this head or page size")
+    if variant != "cp_async" and not (d in (64, 128, 256) and ps >= 8 and 128 % ps == 0):
+        pytest.skip(f"the {variant} variant does not take this head or page size")
+    if variant == "persistent" and nh // nkv > 16:
+        pytest.skip("the persistent variant takes at most 16 heads per kv head")
     ctxs = [1, 127, 128, 129, 300, 1000, 45]
     qlens = [1] * len(ctxs)
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
@@ -239,6 +241,30 @@ def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike, v
     for r in (5, 2, 4):
         assert torch.equal(out2[r], out[r])
     assert float(out2[0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [
+    (8, 4, 128, 16, None), (12, 4, 64, 32, 700), (4, 2, 256, 8, None), (16, 1, 128, 128, None)])
+def test_decode_attention_persistent_ring_wraps(cuda_device, nh, nkv, d, ps, window):
+    """So many (row, kv head, split) items that every resident CTA takes more of them than its
+    ring of tile slots holds, with rows of very different lengths; compared with the plain
+    result and, bit for bit, with the one-CTA-per-split kernel's partial sums merged the
+    same way."""
+    from binfer_b200.csrc import ops
+    ctxs = [2900, 1, 1500, 130, 3001, 777, 2048, 64, 2500, 3, 1999, 2300] * 2
+    qlens = [1] * len(ctxs)
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   qlens, window, True, seed=11)
+    err = _err(cuda_device)
+    out = torch.zeros_like(q)
+    ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, window,
+                         d ** -0.5, max(ctxs), err, variant="persistent")
+    assert int(err.item()) == 0
+    _close(out, ref, BF16)
+    again = torch.zeros_like(q)
+    ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, again, nh, nkv, d, window,
+                         d ** -0.5, max(ctxs), err, variant="persistent")
+    assert torch.equal(out, again), "the result depends on timing"
 
 
 # ------------------------------------------------------------------------ sampling
