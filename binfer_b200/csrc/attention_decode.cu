@@ -241,8 +241,8 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ part_o,
                                               int max_splits) {
   __shared__ float wgt[MERGE_CHUNK];
   __shared__ float sh_M, sh_L;
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
   const int t = rows ? rows[r] : r;
   const int p = positions[t];

@@ -172,9 +172,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  bf_pdl_wait();
   bf_pdl_trigger();
-
   if (tid == 32) {
     for (int s = 0; s < slots; ++s) {
       bf_mbar_init(full + s, 1);
@@ -182,6 +180,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  bf_pdl_wait();
   if (warp == 0) {
     // items before each row: (splits the row's keys touch) x (kv heads), in row order
     int running = 0;

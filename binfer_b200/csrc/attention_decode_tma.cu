@@ -53,8 +53,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + HALVES * HALF_ELEMS);   // [2]: K, V
   float* red_far = reinterpret_cast<float*>(bars + 2);                      // merge buffer if G > 16
 
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
   const int t = rows ? rows[r] : r;
   const int p = positions[t];

@@ -60,9 +60,13 @@ static inline int bf_launch_status() { return (int)cudaGetLastError(); }
 // A kernel launched through bf_launch_pdl may be scheduled while its predecessor on the
 // stream is still running (its blocks become resident, its prologue runs), which hides the
 // launch latency between the short kernels of a decode step.  Such a kernel must call
-// bf_pdl_wait() before it touches global memory: the call returns when every earlier grid
-// has completed and its writes are visible.  bf_pdl_trigger() lets the kernel after this one
-// be scheduled early in turn.  Launched the ordinary way, both calls do nothing.
+// bf_pdl_wait() before it touches global memory that an earlier kernel writes or reads: the
+// call returns when every earlier grid has completed and its writes are visible.  Every
+// thread calls it, on every path, so that "this grid has completed" implies the same of all
+// grids before it.  bf_pdl_trigger(), called first, lets the kernel after this one be
+// scheduled in turn (it then sits in its own wait).  What a kernel does between the two
+// (barrier and tensor-memory set-up, fetching weights, which no kernel of a step writes)
+// overlaps the kernels before it.  Launched the ordinary way, both calls do nothing.
 __device__ __forceinline__ void bf_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void bf_pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -28,8 +28,8 @@ template <typename W>
 __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int vocab, float scale,
                                     int* __restrict__ err) {
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * H;
@@ -95,8 +95,8 @@ __global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid,
                                             const int* __restrict__ rows, int H, float eps,
                                             int write_back) {
   __shared__ float scratch[33];
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * H;
@@ -231,8 +231,8 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
 // bf16, I a multiple of 8: eight elements per thread with 16-byte loads and stores.
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
                                          __nv_bfloat16* __restrict__ out, int T, int I) {
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int per_row = I / 8;
   const size_t n = (size_t)T * per_row;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -281,8 +281,8 @@ BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype
 // input tokens without a trip through the host.
 __global__ void copy_ids_kernel(int* __restrict__ dst, const int* __restrict__ src,
                                 const int* __restrict__ pairs, int n) {
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[pairs[2 * i]] = src[pairs[2 * i + 1]];
 }

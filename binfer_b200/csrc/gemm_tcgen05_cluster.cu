@@ -115,14 +115,27 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // barriers and tensor memory are set up; only now does the kernel need its inputs
+  // Barriers and tensor memory are set up.  The weights do not depend on the kernel before
+  // this one, so the first ring of weight tiles is asked for before waiting for it: when
+  // this kernel was launched early (programmatic dependent launch) they stream in while the
+  // predecessor finishes.  The activations are fetched after the wait.
+  const int pre = min(STAGES, kc1 - kc0);
+  if (warp == 2 && lane == 0) {
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(full + i, stage_bytes);
+      tma_load_2d(tiles + (size_t)i * stage_bytes + a_bytes, &map_w, full + i, (kc0 + i) * BK,
+                  tile * p.bn);
+    }
+  }
   bf_pdl_wait();
 
   if (warp == 2) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kc = kc0; kc < kc1; ++kc) {
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(tiles + (size_t)i * stage_bytes, &map_x, full + i, (kc0 + i) * BK, 0);
+      int stage = pre == STAGES ? 0 : pre;
+      uint32_t phase = pre == STAGES ? 1 : 0;
+      for (int kc = kc0 + pre; kc < kc1; ++kc) {
         if (!mbar_wait(empty + stage, phase ^ 1, abort)) break;
         uint8_t* dst = tiles + (size_t)stage * stage_bytes;
         mbar_expect_tx(full + stage, stage_bytes);

@@ -90,8 +90,8 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
     float eps, int* __restrict__ err) {
   constexpr int D = 128;
   __shared__ float sn_s[64], cs_s[64];
-  bf_pdl_wait();
   bf_pdl_trigger();
+  bf_pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x;
   if (threadIdx.x < 64) {
