@@ -5,20 +5,24 @@
 // coming from the paged bf16 cache.  Two CTAs share an SM, so that one's softmax runs
 // while the other's products occupy the tensor cores:
 //
-//   warp 4      TMA producer: the Q tile once; per key tile one cp.async.bulk.tensor copy
+//   warp 8      TMA producer: the Q tile once; per key tile one cp.async.bulk.tensor copy
 //               per (page, 64 columns) of K and of V into 128-byte-swizzled shared memory,
 //               two key tiles in flight;
-//   warp 5      one thread issues tcgen05.mma: S = Q K^T (M = 128 queries, N = 64 keys,
-//               K = head size) into tensor memory, and, once the probabilities are written,
-//               O_tile = P V (M = 128, N = head size, K = 64 keys; V is read as stored,
-//               an MN-major operand);
-//   warps 0-3   softmax: thread r owns query row r = TMEM lane r.  It reads its row of S
-//               (tcgen05.ld), masks, keeps the running maximum and sum in float with exp2,
-//               writes P as bf16 into the swizzled A-operand tile (over the K tile, which
-//               is dead by then, when the head size is 128), then adds O_tile into its
-//               float accumulators with the running rescale.
+//   warp 9      one thread issues tcgen05.mma: S = Q K^T (M = 128 queries, N = 64 keys,
+//               K = head size) into one of two S buffers in tensor memory, and, once the
+//               probabilities are written, O += P V (M = 128, N = head size, K = 64 keys;
+//               V is read as stored, an MN-major operand).  O stays in tensor memory over
+//               all key tiles;
+//   warps 0-7   softmax, two threads per query row (row r = TMEM lane r; warps w and w + 4
+//               read the same lanes): each reads 32 of the tile's 64 scores (tcgen05.ld),
+//               masks, the two exchange their maxima through shared memory, write their
+//               halves of P as bf16 into the swizzled A-operand tile (over the K tile, which
+//               is dead by then, when the head size is 128) and keep their halves of the
+//               row's sum.  The exponent's reference follows the running maximum only when
+//               that has grown by more than 8; only then is O read, scaled and written
+//               back (tcgen05.ld / st), each thread its half of the columns.
 //
-// S of the next tile is multiplied while the softmax warps still add O of this one.
+// S of the next tile is multiplied while the softmax warps work on this one.
 // The reference's prefill attention is scalar, over whole prompts' fresh keys only
 // (cuda/kernels/bf16_kernels.cu:873-1024); the engine's first kernel for this job is
 // attention_prefill.cu (mma.sync), which stays for the sizes this one does not take:
@@ -40,7 +44,9 @@ namespace {
 
 constexpr int AU_BM = 128;       // queries per CTA
 constexpr int AU_BN = 64;        // keys per tile
-constexpr int AU_THREADS = 192;
+constexpr int AU_THREADS = 320;   // eight softmax warps, the TMA warp, the MMA warp
+constexpr int AU_TMA_WARP = 8;
+constexpr int AU_MMA_WARP = 9;
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -54,6 +60,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
+          taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+      "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+      "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+      "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
 }
 
 // 2^x by the special-function unit (x <= 0 here; -inf gives 0)
@@ -75,6 +95,20 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 
+// Barrier among the 256 softmax threads that also ANDs a predicate.
+__device__ __forceinline__ bool softmax_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "barrier.cta.red.and.pred p, 1, 256, q;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)ok)
+      : "memory");
+  return r != 0;
+}
+
 template <int D>
 __global__ void __launch_bounds__(AU_THREADS, 2)
 prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -91,21 +125,23 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
   constexpr int KV_BYTES = HALVES * KHALF_BYTES;         // one K (or V) tile of 64 keys
   constexpr int P_BYTES = AU_BM * 128;                   // 128 queries x 64 keys
   constexpr bool P_OVER_K = KV_BYTES >= P_BYTES;         // P may lie over the dead K tile
-  constexpr int TMEM_COLS = 256;                         // S: 64 columns, O tile: D columns
+  constexpr int TMEM_COLS = 256;                         // S twice 64 columns, O: D columns
+  constexpr int OH = D / 2;                              // O columns per softmax thread
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* Qs = base;
   uint8_t* Ks = Qs + Q_BYTES;                            // [2][KV_BYTES]
   uint8_t* Vs = Ks + 2 * KV_BYTES;                       // [2][KV_BYTES]
   uint8_t* Psep = Vs + 2 * KV_BYTES;                     // used only when P cannot lie over K
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Psep + (P_OVER_K ? 0 : P_BYTES));
+  float* xm = reinterpret_cast<float*>(Psep + (P_OVER_K ? 0 : P_BYTES));   // [3][2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xm + 3 * 256);
   uint64_t* q_full = bars;             // [1]
   uint64_t* kv_full = bars + 1;        // [2]
   uint64_t* kv_empty = bars + 3;       // [2]
-  uint64_t* s_full = bars + 5;         // [1]
-  uint64_t* p_full = bars + 6;         // [1]  128 arrivals
-  uint64_t* o_full = bars + 7;         // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_full = bars + 5;         // [2]  one per S buffer
+  uint64_t* p_full = bars + 7;         // [1]  256 arrivals
+  uint64_t* o_done = bars + 8;         // [1]  completes once per key tile, after its P V
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int* it = items + 4 * blockIdx.z;
@@ -128,14 +164,14 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < 2; ++s) {
       mbar_init(kv_full + s, 1);
       mbar_init(kv_empty + s, 1);
+      mbar_init(s_full + s, 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
+    mbar_init(p_full, 256);
+    mbar_init(o_done, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == AU_MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
@@ -146,9 +182,9 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + AU_BN;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * AU_BN;
 
-  if (warp == 4) {
+  if (warp == AU_TMA_WARP) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       mbar_expect_tx(q_full, Q_BYTES);
@@ -157,14 +193,10 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
         tma_load_2d(Qs + hh * QHALF_BYTES, &map_q, q_full, h * D + hh * 64, row0 + qt * AU_BM);
     }
     uint32_t phase = 0;
-    for (int kt = kt_first; kt <= kt_last && !*abort; ++kt) {
-      const int buf = (kt - kt_first) & 1;
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(kv_empty + buf, phase ^ 1, abort);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
+    // the page ids of a tile are looked up one tile ahead of its copies
+    auto lookup = [&](int kt, bool& wanted) {
       const int jp = kt * AU_BN + lane * page_size;
-      const bool wanted = lane < pages && jp <= p_last && jp + page_size > j_lo;
+      wanted = kt <= kt_last && lane < pages && jp <= p_last && jp + page_size > j_lo;
       int page = 0;
       if (wanted) {
         page = table[jp / page_size];
@@ -173,6 +205,19 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
           page = 0;
         }
       }
+      return page;
+    };
+    bool wanted_next;
+    int page_next = lookup(kt_first, wanted_next);
+    for (int kt = kt_first; kt <= kt_last && !*abort; ++kt) {
+      const int buf = (kt - kt_first) & 1;
+      const int page = page_next;
+      const bool wanted = wanted_next;
+      page_next = lookup(kt + 1, wanted_next);
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(kv_empty + buf, phase ^ 1, abort);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
       // V rows of pages that are not fetched must read as zero
       uint8_t* vb = Vs + buf * KV_BYTES;
       for (int pg = 0; pg < pages; ++pg) {
@@ -201,7 +246,7 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       if (buf == 1) phase ^= 1;
     }
-  } else if (warp == 5) {
+  } else if (warp == AU_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // S: a = Q (K-major), b = K tile (K-major), N = 64 keys
@@ -210,23 +255,34 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
       // O: a = P (K-major), b = V as stored (MN-major), N = head size
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                ((uint32_t)(D >> 3) << 17) | ((uint32_t)(AU_BM >> 4) << 24);
-      bool ok = mbar_wait(q_full, 0, abort);
-      uint32_t kv_phase = 0, p_phase = 0;
-      for (int kt = kt_first; kt <= kt_last && ok; ++kt) {
-        const int buf = (kt - kt_first) & 1;
-        if (!(ok = mbar_wait(kv_full + buf, kv_phase, abort))) break;
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks + buf * KV_BYTES);
+      const uint32_t q_addr = smem_u32(Qs);
+      auto issue_s = [&](int n) {                        // S of the n-th tile into S buffer n & 1
+        const uint32_t k_addr = smem_u32(Ks + (n & 1) * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t qo = (uint32_t)((k >> 2) * QHALF_BYTES + (k & 3) * 32);
           const uint32_t ko = (uint32_t)((k >> 2) * KHALF_BYTES + (k & 3) * 32);
-          umma_bf16(tmem_s, umma_desc_k_sw128(q_addr + qo), umma_desc_k_sw128(k_addr + ko),
-                    idesc_s, k > 0 ? 1u : 0u);
+          umma_bf16(tmem_s + (uint32_t)((n & 1) * AU_BN), umma_desc_k_sw128(q_addr + qo),
+                    umma_desc_k_sw128(k_addr + ko), idesc_s, k > 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
-        if (!(ok = mbar_wait(p_full, p_phase, abort))) break;
-        p_phase ^= 1;
+        umma_commit(s_full + (n & 1));
+      };
+      const int tiles = kt_last - kt_first + 1;
+      bool ok = mbar_wait(q_full, 0, abort) && mbar_wait(kv_full, 0, abort);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int n = 0; n < tiles && ok; ++n) {
+        const int buf = n & 1;
+        if (n + 1 < tiles) {
+          // S of the next tile runs under the softmax of this one; its buffer is free since
+          // the softmax threads signalled P of the tile before this one
+          if (!(ok = mbar_wait(kv_full + ((n + 1) & 1), ((n + 1) >> 1) & 1, abort))) break;
+          tc_fence_after();
+          issue_s(n + 1);
+        }
+        if (!(ok = mbar_wait(p_full, n & 1, abort))) break;
         tc_fence_after();
         const uint32_t p_addr = smem_u32(P_OVER_K ? Ks + buf * KV_BYTES : Psep);
         const uint32_t v_addr = smem_u32(Vs + buf * KV_BYTES);
@@ -235,129 +291,145 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
           // 16 keys further: along K inside P's swizzled rows, two 8-row groups down in V
           umma_bf16(tmem_o, umma_desc_k_sw128(p_addr + (uint32_t)(k * 32)),
                     umma_desc_mn_sw128(v_addr + (uint32_t)(k * 2048), KHALF_BYTES), idesc_o,
-                    k > 0 ? 1u : 0u);
+                    (n > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(kv_empty + buf);       // K, V (and P) of this tile are free when done
-        umma_commit(o_full);
-        if (buf == 1) kv_phase ^= 1;
+        umma_commit(o_done);
       }
     }
   } else {
     // --------------------------------------------------------------------- softmax
-    const int r = threadIdx.x;                           // query row of the tile = TMEM lane
+    // Two threads per query row: warps 0-3 take keys 0..31 of a tile and the lower half of
+    // O's columns, warps 4-7 keys 32..63 and the upper half (a warp reads the TMEM lanes
+    // 32 * (warp % 4) onwards).  O stays in tensor memory across the tiles.  It, and the
+    // running sum, refer to m_ref, which follows the running maximum only when that has
+    // grown by more than 8 (a factor 256 in the probabilities, harmless in bf16 and float):
+    // only then is O read, scaled and written back, and only by the warps that hold such a row.
+    const int wq = warp & 3, half = warp >> 2;
+    const int r = wq * 32 + lane;                        // query row of the tile = TMEM lane
     const int l = qt * AU_BM + r;                        // index inside the portion
     const bool valid = l < qlen;
     const int pr = pos0 + l;
     const int jl = window > 0 ? max(0, pr - window + 1) : 0;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    float m = -INFINITY, lsum = 0.f;
-    float acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
-    uint32_t s_phase = 0, o_phase = 0;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const uint32_t my_o = tmem_o + lane_addr + (uint32_t)(half * OH);
+    float m_ref = -INFINITY, lsum = 0.f;
     bool alive = true;
-    for (int kt = kt_first; kt <= kt_last; ++kt) {
-      const bool ok = alive && !*abort && mbar_wait(s_full, s_phase, abort);
-      s_phase ^= 1;
-      if (!epilogue_all(ok)) {
+    int n = 0;
+    for (int kt = kt_first; kt <= kt_last; ++kt, ++n) {
+      const bool ok = !*abort && mbar_wait(s_full + (n & 1), (n >> 1) & 1, abort);
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld32(tmem_s + lane_addr + (uint32_t)((n & 1) * AU_BN + half * 32), v);
+      const int t_lo = kt * AU_BN + half * 32;           // first key of this thread's columns
+      const bool need_mask = !valid || t_lo + 31 > pr || t_lo < jl;
+      const int hi = valid ? pr - t_lo : -1;             // last visible column
+      const int lo = jl - t_lo;                          // first visible column
+      float tmax = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j >= lo && j <= hi) tmax = fmaxf(tmax, __uint_as_float(v[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(v[j]));
+      }
+      tmax *= scale_log2;                                // the scale is positive
+      float* x = xm + (n & 1) * 256;
+      x[half * 128 + r] = tmax;
+      if (!softmax_all(ok)) {
         alive = false;
         break;
       }
-      tc_fence_after();
-      uint8_t* Ps = P_OVER_K ? Ks + ((kt - kt_first) & 1) * KV_BYTES : Psep;
-      const int t_lo = kt * AU_BN;
-      const bool need_mask = !valid || t_lo + AU_BN - 1 > pr || t_lo < jl;
-      // pass 1: the row's maximum over this tile.  (The chunk loops are kept rolled: fully
-      // unrolled, the softmax no longer fits the instruction cache and runs many times slower.)
-      const int hi = valid ? pr - t_lo : -1;             // last visible key of the tile
-      const int lo = jl - t_lo;                          // first visible key of the tile
-      float tmax = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < AU_BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + lane_addr + c0, v);
-        if (need_mask) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (c0 + j >= lo && c0 + j <= hi) tmax = fmaxf(tmax, __uint_as_float(v[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(v[j]));
-        }
+      tmax = fmaxf(tmax, x[(half ^ 1) * 128 + r]);       // both threads of the row now agree
+      float factor = 1.f;
+      bool rescale = false;
+      if (tmax > m_ref + 8.f) {                          // also the first finite maximum
+        rescale = m_ref != -INFINITY;                    // before it, O and the sum are zero
+        factor = rescale ? exp2f(m_ref - tmax) : 0.f;
+        m_ref = tmax;
       }
-      tmax *= scale_log2;                                // the scale is positive
-      const float m_new = fmaxf(m, tmax);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = m == -INFINITY ? 0.f : exp2f(m - m_use);
-      m = m_new;
-      // pass 2: probabilities, their sum, and P as bf16 in the swizzled operand tile
-      float tsum = 0.f;
+      if (n > 0 && __any_sync(0xffffffffu, rescale)) {
+        // P V of the tile before must be complete; the warp goes on as one
+        if (__all_sync(0xffffffffu, mbar_wait(o_done, (n - 1) & 1, abort))) {
+          tc_fence_after();
+          const float f = rescale ? factor : 1.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < AU_BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + lane_addr + c0, v);
-        uint32_t packed[16];
+          for (int c0 = 0; c0 < OH; c0 += 32) {
+            uint32_t w[32];
+            tmem_ld32(my_o + c0, w);
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float e0 = ex2_approx(fmaf(__uint_as_float(v[j]), scale_log2, -m_use));
-          float e1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), scale_log2, -m_use));
-          if (need_mask) {
-            if (c0 + j < lo || c0 + j > hi) e0 = 0.f;
-            if (c0 + j + 1 < lo || c0 + j + 1 > hi) e1 = 0.f;
+            for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(w[j]) * f);
+            tmem_st32(my_o + c0, w);
           }
-          tsum += e0 + e1;
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
-          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&p2);
-        }
-        // 32 keys = four 16-byte chunks of this row
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int c = (c0 >> 3) + q4;                  // chunk index along the 64 keys
-          uint8_t* dst = Ps + r * 128 + ((c ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1],
-                                                      packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      lsum = lsum * corr + tsum;
+      lsum *= factor;
+      if (!P_OVER_K && n > 0) mbar_wait(o_done, (n - 1) & 1, abort);   // P of the tile before was read
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      uint8_t* Ps = P_OVER_K ? Ks + (n & 1) * KV_BYTES : Psep;
+      float tsum = 0.f;
+      uint32_t packed[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float e0 = ex2_approx(fmaf(__uint_as_float(v[j]), scale_log2, -m_use));
+        float e1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), scale_log2, -m_use));
+        if (need_mask) {
+          if (j < lo || j > hi) e0 = 0.f;
+          if (j + 1 < lo || j + 1 > hi) e1 = 0.f;
+        }
+        tsum += e0 + e1;
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
+        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&p2);
+      }
+      // 32 keys = four 16-byte chunks of this row
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int c = half * 4 + q4;                     // chunk index along the 64 keys
+        uint8_t* dst = Ps + r * 128 + ((c ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1],
+                                                    packed[4 * q4 + 2], packed[4 * q4 + 3]);
+      }
+      lsum += tsum;
       // P is read by the tensor core through the async proxy
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(p_full);
-      // O of this tile
-      const bool ok2 = mbar_wait(o_full, o_phase, abort);
-      o_phase ^= 1;
-      if (!epilogue_all(ok2)) {
-        alive = false;
-        break;
-      }
+    }
+    // the row's sum from both halves, then O
+    bool ok = alive && !*abort && mbar_wait(o_done, (n - 1) & 1, abort);
+    float* xl = xm + 512;
+    xl[half * 128 + r] = lsum;
+    ok = softmax_all(ok);
+    if (ok) {
       tc_fence_after();
+      const float inv = 1.f / (xl[r] + xl[128 + r]);
+      __nv_bfloat16* dst = out + ((size_t)(row0 + l) * nh + h) * D + half * OH;
+#pragma unroll 1
+      for (int c0 = 0; c0 < OH; c0 += 32) {
+        uint32_t w[32];
+        tmem_ld32(my_o + c0, w);                         // the whole warp loads; valid rows store
+        if (valid) {
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_addr + c0, v);
+          for (int c = 0; c < 32; c += 8) {
+            uint4 o4;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c0 + j] = acc[c0 + j] * corr + __uint_as_float(v[j]);
-      }
-      tc_fence_before();
-    }
-    if (alive && valid) {
-      const float inv = 1.f / lsum;
-      __nv_bfloat16* dst = out + ((size_t)(row0 + l) * nh + h) * D;
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 8) {
-        uint4 o4;
-        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          o2[j] = __floats2bfloat162_rn(acc[c0 + 2 * j] * inv, acc[c0 + 2 * j + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + c0) = o4;
+            for (int j = 0; j < 4; ++j)
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(w[c + 2 * j]) * inv,
+                                            __uint_as_float(w[c + 2 * j + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + c) = o4;
+          }
+        }
       }
     }
+    tc_fence_before();
   }
 
   __syncthreads();
   if (*abort && threadIdx.x == 0) atomicOr(err, BF_ERR_WAIT);
-  if (warp == 5) {
+  if (warp == AU_MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
@@ -382,7 +454,7 @@ int launch_umma(const void* q, const void* k_cache, const void* v_cache, const i
   constexpr int HALVES = D / 64;
   // Q, two stages of K and V, P apart only when it does not fit over a K tile, barriers
   const size_t smem = 1024 + (size_t)HALVES * 16384 + (size_t)4 * HALVES * 8192 +
-                      (HALVES * 8192 >= 16384 ? 0 : 16384) + 128;
+                      (HALVES * 8192 >= 16384 ? 0 : 16384) + 3 * 1024 + 128;
   auto kern = prefill_attention_umma_kernel<D>;
   static bool configured = false;
   if (!configured) {
