@@ -227,76 +227,91 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ q,
   }
 }
 
-// Merge the splits of each (row, head) in ascending order and normalise.  One block per
-// (row, head): the splits' maxima and sums are reduced by the first warp, each split's
-// weight exp2(m_s - M) is parked in shared memory, and every thread then walks the splits
-// for its output columns with several loads in flight.
-#define MERGE_CHUNK 256
+// Merge the splits of each (row, head) in ascending order and normalise.  One block of 128
+// threads per (row, head).  The kernel is all latency (a few KB from L2 per block), so it is
+// built around the number of dependent round trips: the row's position and, speculatively,
+// each thread's split's (m, l) pair are asked for together; the weights exp2(m_s - M) go to
+// shared memory; then every thread asks for the partial outputs of its column for 32 splits
+// at once.  Sums run in one fixed order (ascending splits per thread, then threads).  Its
+// shared memory is kept to half a KB so that its blocks fit beside the attention kernel's,
+// which leave little: the blocks are then resident (and have triggered their dependents)
+// before the attention ends.
+#define MERGE_PASS 128
 template <int D>
-__global__ void decode_attention_merge_kernel(const float* __restrict__ part_o,
-                                              const float* __restrict__ part_ml,
-                                              const int* __restrict__ rows,
-                                              const int* __restrict__ positions,
-                                              __nv_bfloat16* __restrict__ out, int nh, int window,
-                                              int max_splits) {
-  __shared__ float wgt[MERGE_CHUNK];
-  __shared__ float sh_M, sh_L;
+__global__ void __launch_bounds__(128)
+decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                              const int* __restrict__ rows, const int* __restrict__ positions,
+                              __nv_bfloat16* __restrict__ out, int nh, int window,
+                              int max_splits) {
+  __shared__ float wgt[MERGE_PASS];
+  __shared__ float red[4];
   bf_pdl_trigger();
   bf_pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t base = ((size_t)r * nh + h) * max_splits;
+  const float2* ml2 = reinterpret_cast<const float2*>(part_ml) + base;
   const int t = rows ? rows[r] : r;
+  const float2 ml0 = tid < max_splits ? __ldcg(ml2 + tid) : make_float2(-INFINITY, 0.f);
   const int p = positions[t];
   const int j0 = window > 0 ? max(0, p - window + 1) : 0;
   const int s_first = j0 / DEC_SPLIT, s_last = p / DEC_SPLIT;
-  const size_t base = ((size_t)r * nh + h) * max_splits;
-  const int lane = threadIdx.x & 31;
-  if (threadIdx.x < 32) {
-    float M = -INFINITY;
-    for (int s = s_first + lane; s <= s_last; s += 32) M = fmaxf(M, __ldcg(part_ml + (base + s) * 2));
-    M = warp_max(M);
-    float L = 0.f;      // lanes sum disjoint splits; the order of this sum is fixed by (p, window)
-    for (int s = s_first + lane; s <= s_last; s += 32)
-      L += __ldcg(part_ml + (base + s) * 2 + 1) * exp2f(__ldcg(part_ml + (base + s) * 2) - M);
-    L = warp_sum(L);
-    if (lane == 0) {
-      sh_M = M;
-      sh_L = L;
-    }
-  }
+  // thread tid owns the splits tid, tid + 128, ...; the first came with the position
+  float m_loc = -INFINITY;
+  for (int s = tid; s <= s_last; s += 128)
+    if (s >= s_first) m_loc = fmaxf(m_loc, (s == tid ? ml0 : __ldcg(ml2 + s)).x);
+  m_loc = warp_max(m_loc);
+  if (lane == 0) red[warp] = m_loc;
   __syncthreads();
-  const float M = sh_M, inv = 1.f / sh_L;
-  float acc[(D + 127) / 128];
+  const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float l_loc = 0.f;
+  for (int s = tid; s <= s_last; s += 128)
+    if (s >= s_first) {
+      const float2 ml = s == tid ? ml0 : __ldcg(ml2 + s);
+      const float w = exp2f(ml.x - M);
+      if (s - s_first < MERGE_PASS) wgt[s - s_first] = w;
+      l_loc += ml.y * w;
+    }
+  l_loc = warp_sum(l_loc);
+  if (lane == 0) red[warp] = l_loc;
+  __syncthreads();                                       // also: the weights are in place
+  const float inv = 1.f / (((red[0] + red[1]) + red[2]) + red[3]);
+
+  constexpr int COLS = (D + 127) / 128;
+  float acc[COLS];
 #pragma unroll
-  for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = 0.f;
-  for (int c0 = s_first; c0 <= s_last; c0 += MERGE_CHUNK) {
-    const int n = min(MERGE_CHUNK, s_last - c0 + 1);
-    __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x)
-      wgt[i] = exp2f(__ldcg(part_ml + (base + c0 + i) * 2) - M);
-    __syncthreads();
+  for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
+  const int n = s_last - s_first + 1;
+  for (int p0 = 0; p0 < n; p0 += MERGE_PASS) {
+    const int np = min(MERGE_PASS, n - p0);
+    if (p0 > 0) {                                        // contexts of more than 16384 keys
+      __syncthreads();
+      for (int i = tid; i < np; i += 128) wgt[i] = exp2f(__ldcg(ml2 + s_first + p0 + i).x - M);
+      __syncthreads();
+    }
 #pragma unroll
-    for (int i = 0; i < (D + 127) / 128; ++i) {
-      const int c = threadIdx.x + i * 128;
+    for (int i = 0; i < COLS; ++i) {
+      const int c = tid + i * 128;
       if (c < D) {
-        const float* po = part_o + (base + c0) * D + c;
+        const float* po = part_o + (base + s_first + p0) * D + c;
         float a = acc[i];
-        int s = 0;
-        for (; s + 4 <= n; s += 4) {
-          const float v0 = __ldcg(po + (size_t)s * D), v1 = __ldcg(po + (size_t)(s + 1) * D);
-          const float v2 = __ldcg(po + (size_t)(s + 2) * D), v3 = __ldcg(po + (size_t)(s + 3) * D);
-          a += v0 * wgt[s];
-          a += v1 * wgt[s + 1];
-          a += v2 * wgt[s + 2];
-          a += v3 * wgt[s + 3];
+        for (int c0 = 0; c0 < np; c0 += 32) {
+          float v[32];
+#pragma unroll
+          for (int u = 0; u < 32; ++u)
+            v[u] = c0 + u < np ? __ldcg(po + (size_t)(c0 + u) * D) : 0.f;
+#pragma unroll
+          for (int u = 0; u < 32; ++u)
+            if (c0 + u < np) a += v[u] * wgt[c0 + u];
         }
-        for (; s < n; ++s) a += __ldcg(po + (size_t)s * D) * wgt[s];
         acc[i] = a;
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < (D + 127) / 128; ++i) {
-    const int c = threadIdx.x + i * 128;
+  for (int i = 0; i < COLS; ++i) {
+    const int c = tid + i * 128;
     if (c < D) out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(acc[i] * inv);
   }
 }

@@ -8,8 +8,11 @@ in, ``CUBLAS_COMPUTE_32F``).  Which one: ``BINFER_B200_GEMM=own`` takes the engi
 kernel for every shape it accepts, ``library`` never, and ``auto`` (the default)
 where it was measured to be at least as fast as the library on a B200: at most 128
 tokens against a very wide weight (the output head while decoding), and at most 16
-tokens against a weight of at most 4096 output features, where the split-K cluster
-kernel (``csrc/gemm_tcgen05_cluster.cu``) runs (the output and down projections).
+tokens against a weight of at most 8192 output features, where the split-K cluster
+kernel (``csrc/gemm_tcgen05_cluster.cu``) runs (the qkv, output and down projections).
+Alone, the cluster kernel ties with the library on the qkv projection; inside a decode
+step it wins, because it is launched as a programmatic dependent of the kernel before
+it and has its first weight tiles under way when that kernel ends.
 """
 from __future__ import annotations
 
@@ -43,7 +46,7 @@ def _use_own(M: int, N: int, K: int) -> bool:
 def _use_cluster(M: int, N: int, K: int) -> bool:
     if _POLICY == "library" or M > 16:
         return False
-    return N <= 4096 and K >= 2048 if _POLICY == "auto" else N <= 8192
+    return N <= 8192 and (K >= 2048 or _POLICY == "own")
 
 
 _plans = {}
