@@ -276,7 +276,9 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
 }  // namespace
 
 // Tile width and cluster size for `features` x K on `num_sms` SMs.  Clusters of 4 measured
-// best on a B200 (8 schedules worse, 2 leaves too few CTAs); the tile width (a multiple of
+// best on a B200 (8 schedules worse, 2 leaves too few CTAs); a weight wide enough to give
+// nearly every SM a tile of its own (the gate/up projection) takes "clusters" of one CTA,
+// which is the same kernel without a split; the tile width (a multiple of
 // 16 per CTA of the cluster, at most 256 feature rows) is the one that brings the number of
 // CTAs closest to, and not above, the SM count, each CTA keeping at least 4 K-steps.
 // Returns the number of CTAs, or 0 (outputs untouched) when no split is worth it.
@@ -284,8 +286,8 @@ BF_EXPORT int bf_gemm_cluster_plan(int features, int K, int num_sms, int* bn_out
                                    int* cluster_out) {
   const int kc = (K + BK - 1) / BK;
   int best_ctas = 0, best_bn = 0, best_c = 0;
-  const int order[2] = {4, 2};
-  for (int i = 0; i < 2; ++i) {
+  const int order[3] = {4, 2, 1};
+  for (int i = 0; i < 3; ++i) {
     const int c = order[i];
     if (kc / c < 4) continue;
     const int max_ctas = (num_sms / c) * c;
@@ -317,7 +319,7 @@ BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int 
   if (tokens > CL_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
       ((uintptr_t)w & 15))
     return (int)cudaErrorInvalidValue;
-  if ((cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
+  if ((cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
       bn % (16 * cluster))
     return (int)cudaErrorInvalidValue;
   ClusterGemmParams p;

@@ -440,7 +440,8 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
 @pytest.mark.parametrize("M,N,K,bn,c", [(1, 300, 520, 64, 4), (8, 4096, 4096, 128, 4),
                                         (16, 1000, 4104, 128, 8), (7, 6144, 4096, 192, 4),
                                         (3, 256, 256, 256, 2), (16, 4096, 12288, 128, 4),
-                                        (5, 96, 64, 64, 4)])
+                                        (5, 96, 64, 64, 4), (8, 24576, 4096, 176, 1),
+                                        (2, 1000, 320, 80, 1)])
 @pytest.mark.parametrize("out_dtype", [BF16, F32])
 def test_gemm_bf16_cluster_split_k(cuda_device, M, N, K, bn, c, out_dtype):
     """K split over a cluster and reduced through distributed shared memory; widths and depths
