@@ -91,3 +91,40 @@ static inline int bf_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, s
   if (e != cudaSuccess) return (int)e;
   return bf_launch_status();
 }
+
+// ------------------------------------------------------------------ a row factor left out
+// A product whose epilogue also adds into the residual stream and prepares the next norm's
+// output (gemm_tcgen05_cluster.cu) cannot know the row's mean square, which spans all its
+// CTAs.  It leaves x * w_norm and, per row, one partial sum of squares per CTA; the factor
+// rsqrt(sum / width + eps) commutes with the product that follows, so the kernel after
+// that product applies it.  `partials` is [rows, count]; a null pointer means no factor.
+struct BfRowScale {
+  const float* partials;
+  int count;
+  float inv_width, eps;
+};
+// By one warp, in two steps so that the loads of the first can be in flight under other
+// work: every lane fetches its share (up to four values; a row has one partial per CTA of the
+// product, 128 or so), then the shares are summed in one fixed order and every lane gets the
+// factor.
+struct BfRowShare {
+  float v[4];
+};
+__device__ __forceinline__ BfRowShare bf_row_fetch(const BfRowScale& rs, int row, int lane) {
+  BfRowShare sh = {{0.f, 0.f, 0.f, 0.f}};
+  if (!rs.partials) return sh;
+  const float* p = rs.partials + (size_t)row * rs.count;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (lane + 32 * j < rs.count) sh.v[j] = p[lane + 32 * j];
+  for (int i = lane + 128; i < rs.count; i += 32) sh.v[0] += p[i];
+  return sh;
+}
+__device__ __forceinline__ float bf_row_finish(const BfRowScale& rs, const BfRowShare& sh) {
+  if (!rs.partials) return 1.f;
+  const float s = warp_sum(((sh.v[0] + sh.v[1]) + sh.v[2]) + sh.v[3]);
+  return rsqrtf(s * rs.inv_width + rs.eps);
+}
+__device__ __forceinline__ float bf_row_factor(const BfRowScale& rs, int row, int lane) {
+  return bf_row_finish(rs, bf_row_fetch(rs, row, lane));
+}

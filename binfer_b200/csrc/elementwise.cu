@@ -228,6 +228,52 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
   }
 }
 
+// The same when the rows of gu still lack a factor (see BfRowScale).  I is at least 256, so
+// the 32 chunks of a warp lie in at most two rows, whose factors the warp works out itself,
+// its loads of the partial sums in flight together with its loads of gate and up.
+__global__ void silu_mul_bf16_scaled_kernel(const __nv_bfloat16* __restrict__ gu,
+                                            __nv_bfloat16* __restrict__ out, int T, int I,
+                                            BfRowScale rs) {
+  bf_pdl_trigger();
+  bf_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int per_row = I / 8;
+  const size_t n = (size_t)T * per_row;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  // whole warps stay in the loop together: the factor is a warp's work
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31); i0 < n; i0 += step) {
+    const size_t i = i0 + lane;
+    const bool on = i < n;
+    const size_t t = on ? i / per_row : 0, c = on ? (i - t * per_row) * 8 : 0;
+    uint4 g4 = make_uint4(0, 0, 0, 0), u4 = g4;
+    if (on) {
+      g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c);
+      u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
+    }
+    const int t_lo = (int)(i0 / per_row);
+    const size_t i_hi = i0 + 31 < n ? i0 + 31 : n - 1;
+    const int t_hi = (int)(i_hi / per_row);
+    const BfRowShare s_lo = bf_row_fetch(rs, t_lo, lane);
+    float f = bf_row_finish(rs, s_lo);
+    if (t_hi != t_lo) {                                  // uniform over the warp
+      const float f_hi = bf_row_factor(rs, t_hi, lane);
+      if ((int)t == t_hi) f = f_hi;
+    }
+    if (!on) continue;
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      g.x *= f; g.y *= f; u.x *= f; u.y *= f;
+      o2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * I + c) = o4;
+  }
+}
+
 // bf16, I a multiple of 8: eight elements per thread with 16-byte loads and stores.
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
                                          __nv_bfloat16* __restrict__ out, int T, int I) {
@@ -252,6 +298,23 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
     }
     *reinterpret_cast<uint4*>(out + t * I + c) = o4;
   }
+}
+
+// silu(f gate) * (f up) for bf16 rows that still lack the factor f (see BfRowScale): I a
+// multiple of 8 and at least 256; cudaErrorInvalidValue otherwise.
+BF_EXPORT int bf_silu_mul_scaled(const void* gu, void* out, int T, int I,
+                                 const float* row_partials, int row_count, int row_width,
+                                 float row_eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (I % 8 || I < 256 || ((uintptr_t)gu & 15) || ((uintptr_t)out & 15) ||
+      !row_partials || row_count <= 0 || row_width <= 0)
+    return (int)cudaErrorInvalidValue;
+  const BfRowScale rs = {row_partials, row_count, 1.f / (float)row_width, row_eps};
+  const int threads = 256;
+  long long blocks = ((long long)T * (I / 8) + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return bf_launch_pdl(silu_mul_bf16_scaled_kernel, dim3((int)blocks), dim3(threads), 0, stream,
+                       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, rs);
 }
 
 BF_EXPORT int bf_silu_mul(const void* gu, void* out, int T, int I, int act_dtype,

@@ -42,6 +42,14 @@ struct ClusterGemmParams {
   int stages;
   long long ldo;
   int* err;
+  // Fused "add into the residual stream and prepare the next norm" epilogue (resid != null):
+  // resid[t, f] += sum; xt[t, f] = bf16(resid[t, f] * norm_w[f]); and this CTA's part of the
+  // row's sum of squares goes to partials[t, blockIdx.x].  `out` is not written then.
+  float* resid;
+  const float* norm_w;
+  __nv_bfloat16* xt;
+  float* partials;
+  long long ldr, ldxt;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -203,16 +211,55 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     tc_fence_before();
   }
 
+  // the fused epilogue's inputs do not depend on the product: they are asked for before the
+  // cluster waits for its slowest member (up to four elements a thread; more are read later)
+  float pre_r[4], pre_w[4];
+  if (p.resid) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = threadIdx.x + j * blockDim.x;
+      const int t = idx / slice, col = idx - t * slice;
+      const int f = tile * p.bn + rank * slice + col;
+      const bool in = idx < p.tokens * slice && f < p.features;
+      pre_r[j] = in ? p.resid[(size_t)t * p.ldr + f] : 0.f;
+      pre_w[j] = in ? p.norm_w[f] : 0.f;
+    }
+  }
+
   // every thread of every CTA of the cluster: partials are in place after this
   cluster_sync_all();
 
   // this CTA's slice: add the partials in ascending rank order, store
-  for (int idx = threadIdx.x; idx < p.tokens * slice; idx += blockDim.x) {
+  int j = 0;
+  for (int idx = threadIdx.x; idx < p.tokens * slice; idx += blockDim.x, ++j) {
     const int t = idx / slice, col = idx - t * slice;
     float sum = 0.f;
     for (int r = 0; r < p.cluster; ++r) sum += recv[(r * CL_TOKENS + t) * slice + col];
     const int f = tile * p.bn + rank * slice + col;
-    if (f < p.features) bf_st(out + (size_t)t * p.ldo + f, sum);
+    if (!p.resid) {
+      if (f < p.features) bf_st(out + (size_t)t * p.ldo + f, sum);
+    } else {
+      float x = 0.f;
+      if (f < p.features) {
+        float* rp = p.resid + (size_t)t * p.ldr + f;
+        // (the selects keep pre_r and pre_w in registers)
+        const float r0 = j == 0 ? pre_r[0] : j == 1 ? pre_r[1] : j == 2 ? pre_r[2] : pre_r[3];
+        const float w0 = j == 0 ? pre_w[0] : j == 1 ? pre_w[1] : j == 2 ? pre_w[2] : pre_w[3];
+        x = (j < 4 ? r0 : *rp) + sum;
+        *rp = x;
+        p.xt[(size_t)t * p.ldxt + f] = __float2bfloat16_rn(x * (j < 4 ? w0 : p.norm_w[f]));
+      }
+      recv[t * slice + col] = x * x;                     // rank 0's part of recv: read above, by this thread
+    }
+  }
+  if (p.resid) {
+    // one partial sum of squares per token and CTA, its columns added in ascending order
+    __syncthreads();
+    for (int t = threadIdx.x; t < p.tokens; t += blockDim.x) {
+      float sq = 0.f;
+      for (int col = 0; col < slice; ++col) sq += recv[t * slice + col];
+      p.partials[(size_t)t * gridDim.x + blockIdx.x] = sq;
+    }
   }
 
   __syncthreads();
@@ -331,7 +378,50 @@ BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int 
   p.stages = 0;
   p.ldo = ldo;
   p.err = err;
+  p.resid = nullptr;
+  p.norm_w = nullptr;
+  p.xt = nullptr;
+  p.partials = nullptr;
+  p.ldr = p.ldxt = 0;
   return out_dtype == BF_DTYPE_F32
              ? launch_cluster<float>(x, w, (float*)out, p, ldx, ldw, stream)
              : launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)out, p, ldx, ldw, stream);
+}
+
+// The same product with the residual stream and the next norm in its epilogue:
+//   resid[tokens, features] (float) += x * w^T;   xt = bf16(resid * norm_w)   (per feature);
+//   partials[t, c] = CTA c's part of sum_f resid[t, f]^2,  c < the number of CTAs, which is
+//   ceil(features / bn) * cluster and is returned in *n_partials.
+// The norm's output is xt * rsqrt(sum_c partials[t, c] / features + eps): the factor is left
+// to the kernel after the next product (BfRowScale).  No other output is written.
+BF_EXPORT int bf_gemm_bf16_cluster_add_norm(const void* x, const void* w, int tokens, int features,
+                                            int K, long long ldx, long long ldw, int bn,
+                                            int cluster, float* resid, long long ldr,
+                                            const float* norm_w, void* xt, long long ldxt,
+                                            float* partials, int* n_partials, int* err,
+                                            cudaStream_t stream) {
+  if (tokens <= 0 || features <= 0) return 0;
+  if (tokens > CL_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
+      ((uintptr_t)w & 15) || !resid || !norm_w || !xt || !partials)
+    return (int)cudaErrorInvalidValue;
+  if ((cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
+      bn % (16 * cluster))
+    return (int)cudaErrorInvalidValue;
+  ClusterGemmParams p;
+  p.tokens = tokens;
+  p.features = features;
+  p.K = K;
+  p.bn = bn;
+  p.cluster = cluster;
+  p.stages = 0;
+  p.ldo = 0;
+  p.err = err;
+  p.resid = resid;
+  p.norm_w = norm_w;
+  p.xt = (__nv_bfloat16*)xt;
+  p.partials = partials;
+  p.ldr = ldr;
+  p.ldxt = ldxt;
+  if (n_partials) *n_partials = ((features + bn - 1) / bn) * cluster;
+  return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
 }

@@ -137,11 +137,46 @@ def residual_add(resid: torch.Tensor, delta: torch.Tensor) -> None:
                                  _c_int(_dtype_code(delta)), _stream())
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]."""
+class RowScale:
+    """A factor per row that is still to be applied: ``rsqrt(partials[t].sum() / width + eps)``.
+
+    It is what a product that also prepared the next norm (``gemm_bf16_cluster_add_norm``)
+    leaves out, because no CTA of it sees a whole row.  A linear map commutes with the
+    factor, so the kernel after the next product applies it (``qk_norm_rope_kv_write``,
+    ``silu_mul``).  ``partials`` is float32 ``[rows, count]``, contiguous."""
+    __slots__ = ("partials", "width", "eps")
+
+    def __init__(self, partials: torch.Tensor, width: int, eps: float):
+        self.partials, self.width, self.eps = partials, int(width), float(eps)
+
+    def factors(self) -> torch.Tensor:
+        """The factors themselves, float32 ``[rows]`` (for tests and for parts that cannot
+        take a RowScale)."""
+        return torch.rsqrt(self.partials.sum(dim=1) / self.width + self.eps)
+
+
+def _row_scale_args(rs: Optional["RowScale"], rows: int):
+    if rs is None:
+        return _ptr(None), _c_int(0), _c_int(0), _c_float(0.0)
+    p = rs.partials
+    if p.dtype != torch.float32 or not p.is_contiguous() or p.dim() != 2 or p.shape[0] < rows:
+        raise KernelError("row scale: partials must be contiguous float32 [rows, count]")
+    return _ptr(p), _c_int(p.shape[1]), _c_int(rs.width), _c_float(rs.eps)
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor,
+             row_scale: Optional[RowScale] = None) -> None:
+    """out[t, c] = silu(f gate_up[t, c]) * f gate_up[t, I + c]; f = 1 without ``row_scale``
+    (which is taken for bfloat16 and I a multiple of 8, at least 256)."""
     T, I = out.shape
     if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or gate_up.dtype != out.dtype:
         raise KernelError("silu_mul: gate_up must be contiguous [T, 2*I] of the output's dtype")
+    if row_scale is not None:
+        if out.dtype != torch.bfloat16 or I % 8 or I < 256:
+            raise KernelError("silu_mul: a row scale needs bfloat16 and I % 8 == 0, I >= 256")
+        _run("silu_mul_scaled", lib().bf_silu_mul_scaled, _ptr(gate_up), _ptr(out), _c_int(T),
+             _c_int(I), *_row_scale_args(row_scale, T), _stream())
+        return
     _run("silu_mul", lib().bf_silu_mul, _ptr(gate_up), _ptr(out), _c_int(T), _c_int(I),
                              _c_int(_dtype_code(out)), _stream())
 
@@ -158,9 +193,11 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_w: Optional[torch.Tensor],
                           positions: torch.Tensor, slots: Optional[torch.Tensor],
                           q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
                           v_cache: Optional[torch.Tensor], nh: int, nkv: int, d: int,
-                          eps: float, err: torch.Tensor) -> None:
+                          eps: float, err: torch.Tensor,
+                          row_scale: Optional[RowScale] = None) -> None:
     """Per-head RMSNorm of q and k, rotation, q to ``q_out [T, nh*d]``, k and v into
-    cache pages ``[pages, nkv, page_size, d]`` at ``slots``."""
+    cache pages ``[pages, nkv, page_size, d]`` at ``slots``.  With ``row_scale`` the rows of
+    ``qkv`` are first multiplied by their factors."""
     T = qkv.shape[0]
     if qkv.stride(1) != 1:
         raise KernelError("qkv rows must be contiguous")
@@ -173,7 +210,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_w: Optional[torch.Tensor],
         _ptr(qkv), _c_ll(qkv.stride(0)), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _c_int(rot_half),
         _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(T),
         _c_int(nh), _c_int(nkv if k_cache is not None else 0), _c_int(d), _c_int(page_size),
-        _c_ll(num_slots), _c_float(eps), _c_int(_dtype_code(qkv)), _ptr(err), _stream())
+        _c_ll(num_slots), _c_float(eps), _c_int(_dtype_code(qkv)),
+        *_row_scale_args(row_scale, T), _ptr(err), _stream())
 
 
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -355,6 +393,33 @@ def gemm_bf16_cluster(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: 
          _c_int(N), _c_int(K), _c_ll(x.stride(0)), _c_ll(w.stride(0)), _c_ll(out.stride(0)),
          _c_int(_dtype_code(out)), _c_int(bn), _c_int(cluster), _ptr(err), _stream())
     return True
+
+
+def gemm_bf16_cluster_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
+                               norm_w: torch.Tensor, eps: float, err: torch.Tensor, bn: int,
+                               cluster: int):
+    """``resid += x @ w^T`` (float32 stream ``[M, N]``), and the next norm's output short of its
+    row factor: returns ``(xt, RowScale)`` with ``xt = bfloat16(resid * norm_w)``, or None,
+    having done nothing, for shapes the kernel does not take (M <= 16, see
+    ``gemm_bf16_cluster``)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if (M > 16 or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
+            or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16
+            or resid.dtype != torch.float32 or resid.shape != (M, N) or resid.stride(1) != 1
+            or norm_w.dtype != torch.float32 or norm_w.numel() != N or not norm_w.is_contiguous()):
+        return None
+    count = -(-N // bn) * cluster
+    xt = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    partials = torch.empty((M, count), dtype=torch.float32, device=x.device)
+    n = _c_int(0)
+    _run("gemm_bf16_cluster_add_norm", lib().bf_gemm_bf16_cluster_add_norm, _ptr(x), _ptr(w),
+         _c_int(M), _c_int(N), _c_int(K), _c_ll(x.stride(0)), _c_ll(w.stride(0)), _c_int(bn),
+         _c_int(cluster), _ptr(resid), _c_ll(resid.stride(0)), _ptr(norm_w), _ptr(xt),
+         _c_ll(xt.stride(0)), _ptr(partials), ctypes.byref(n), _ptr(err), _stream())
+    if n.value != count:
+        raise KernelError("gemm_bf16_cluster_add_norm: the kernel counts its CTAs differently")
+    return xt, RowScale(partials, N, eps)
 
 
 # -------------------------------------------------------------------- sampling

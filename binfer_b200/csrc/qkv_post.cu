@@ -20,7 +20,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const float* __restrict__ k_w, const float* __restrict__ inv_freq, int rot_half,
     const int* __restrict__ positions, const int* __restrict__ slots, A* __restrict__ q_out,
     A* __restrict__ k_cache, A* __restrict__ v_cache, int nh, int nkv, int d, int page_size,
-    long long num_slots, float eps, int* __restrict__ err) {
+    long long num_slots, float eps, BfRowScale rs, int* __restrict__ err) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -30,9 +30,10 @@ __global__ void qk_norm_rope_kv_write_kernel(
   if (hh >= total) return;
   float* x = sh + (size_t)warp * d;
   const A* src = qkv + (size_t)t * row_stride + (size_t)hh * d;
+  const float row_factor = bf_row_factor(rs, t, lane);
   float ss = 0.f;
   for (int i = lane; i < d; i += 32) {
-    const float v = bf_ld(src + i);
+    const float v = bf_ld(src + i) * row_factor;
     x[i] = v;
     ss += v * v;
   }
@@ -87,13 +88,14 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
     const int* __restrict__ positions, const int* __restrict__ slots,
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
     __nv_bfloat16* __restrict__ v_cache, int nh, int nkv, int page_size, long long num_slots,
-    float eps, int* __restrict__ err) {
+    float eps, BfRowScale rs, int* __restrict__ err) {
   constexpr int D = 128;
   __shared__ float sn_s[64], cs_s[64];
   bf_pdl_trigger();
   bf_pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x;
+  const BfRowShare share = bf_row_fetch(rs, t, lane);    // in flight under the sines and cosines
   if (threadIdx.x < 64) {
     float sn, cs;
     sincosf((float)positions[t] * inv_freq[threadIdx.x], &sn, &cs);
@@ -101,6 +103,7 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
     cs_s[threadIdx.x] = cs;
   }
   __syncthreads();
+  const float row_factor = bf_row_finish(rs, share);
   const int slot = k_cache ? slots[t] : -1;
   const bool upper = lane >= 16;               // holds elements i + 64 of the pairs
   const int fi = (lane & 15) * 4;
@@ -113,7 +116,7 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
                                                       (size_t)hh * D + lane * 4);
     const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
     const float2 a = __bfloat1622float2(r2[0]), b = __bfloat1622float2(r2[1]);
-    float x[4] = {a.x, a.y, b.x, b.y};
+    float x[4] = {a.x * row_factor, a.y * row_factor, b.x * row_factor, b.y * row_factor};
     if (is_q || is_k) {
       if (is_q ? q_w != nullptr : k_w != nullptr) {
         const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
@@ -156,8 +159,12 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
     const void* qkv, long long row_stride, const float* q_w, const float* k_w,
     const float* inv_freq, int rot_half, const int* positions, const int* slots, void* q_out,
     void* k_cache, void* v_cache, int T, int nh, int nkv, int d, int page_size,
-    long long num_slots, float eps, int act_dtype, int* err, cudaStream_t stream) {
+    long long num_slots, float eps, int act_dtype, const float* row_partials, int row_count,
+    int row_width, float row_eps, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
+  // the rows of qkv may still lack a factor (see BfRowScale); it is applied as they are read
+  const BfRowScale rs = {row_partials, row_count, row_width > 0 ? 1.f / (float)row_width : 0.f,
+                         row_eps};
   if (2 * rot_half > d) return (int)cudaErrorInvalidValue;
   const int warps = 4;
   const int total = nh + 2 * nkv;
@@ -170,7 +177,7 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
                          dim3(total >= 16 ? 256 : 128), 0, stream, (const __nv_bfloat16*)qkv,
                          row_stride, q_w, k_w, inv_freq, positions, slots, (__nv_bfloat16*)q_out,
                          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, page_size,
-                         num_slots, eps, err);
+                         num_slots, eps, rs, err);
   }
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
@@ -178,11 +185,11 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
     qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, smem, stream>>>(
         (const float*)qkv, row_stride, q_w, k_w, inv_freq, rot_half, positions, slots,
         (float*)q_out, (float*)k_cache, (float*)v_cache, nh, nkv, d, page_size, num_slots, eps,
-        err);
+        rs, err);
   else
     qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)qkv, row_stride, q_w, k_w, inv_freq, rot_half, positions, slots,
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, d,
-        page_size, num_slots, eps, err);
+        page_size, num_slots, eps, rs, err);
   return bf_launch_status();
 }

@@ -23,7 +23,8 @@ from ..cache.manager import KVNeed
 from ..config.specs import AttentionSpec
 from ..csrc import ops
 from ..weights.loader import ParamSpec
-from .base import (BuildEnv, EntryView, Mixer, StepContext, build_position, register_mixer)
+from .base import (BuildEnv, DeferredLinear, EntryView, Mixer, StepContext, build_position,
+                   register_mixer, split_scaled)
 from .linear import linear
 
 
@@ -70,7 +71,16 @@ class GQAAttention(Mixer):
         return KVNeed(s.num_kv_heads, s.head_dim, s.window)
 
     # ----------------------------------------------------------------- forward
-    def forward(self, x: torch.Tensor, ctx: StepContext, view: EntryView) -> torch.Tensor:
+    accepts_scaled_rows = True
+
+    def forward(self, x, ctx: StepContext, view: EntryView) -> torch.Tensor:
+        return self.forward_deferred(x, ctx, view).compute()
+
+    def forward_deferred(self, x, ctx: StepContext, view: EntryView) -> DeferredLinear:
+        """Everything but the output projection, which is left to the caller (the block
+        fuses it with the add into the stream and the next norm where it can).  ``x`` may be
+        ``ScaledRows``: its factor is applied to the rows of q, k and v as they are read."""
+        x, row_scale = split_scaled(x)
         s, T = self.spec, x.shape[0]
         g = view.group
         if view.writes_cache:
@@ -84,10 +94,10 @@ class GQAAttention(Mixer):
             ctx.positions, ctx.slots[g] if view.writes_cache else None, q,
             view.k_cache if view.writes_cache else None,
             view.v_cache if view.writes_cache else None,
-            s.num_heads, s.num_kv_heads, s.head_dim, s.qk_norm_eps, ctx.err)
+            s.num_heads, s.num_kv_heads, s.head_dim, s.qk_norm_eps, ctx.err, row_scale=row_scale)
         out = torch.empty_like(q)
         self.attend(q, out, ctx, view)
-        return linear(out, self.w_o)
+        return DeferredLinear(out, self.w_o)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext,
                view: EntryView) -> None:

@@ -124,21 +124,77 @@ class EntryView:
     state: Optional[torch.Tensor]      # [slots, *shape] of the mixer's StateNeed
 
 
+class DeferredLinear:
+    """``x @ w^T`` not yet computed: how a part may hand its output to the block
+    (``forward_deferred``), so that the product can be fused with what follows it, the add
+    into the residual stream and the next norm."""
+    __slots__ = ("x", "w")
+
+    def __init__(self, x: torch.Tensor, w: torch.Tensor):
+        self.x, self.w = x, w
+
+    def compute(self) -> torch.Tensor:
+        from .linear import linear
+        return linear(self.x, self.w)
+
+
+class ScaledRows:
+    """Activations ``[T, H]`` whose rows still lack a common factor (``scale``, an
+    ``ops.RowScale``): a norm's output as a fused product leaves it.  A part that sets
+    ``accepts_scaled_rows`` runs its first product on ``tensor`` and hands ``scale`` to the
+    kernel after that product; for any other part the block calls :meth:`dense`."""
+    __slots__ = ("tensor", "scale")
+
+    def __init__(self, tensor: torch.Tensor, scale):
+        self.tensor, self.scale = tensor, scale
+
+    def dense(self) -> torch.Tensor:
+        f = self.scale.factors().unsqueeze(1)
+        return (self.tensor.float() * f).to(self.tensor.dtype)
+
+
+def split_scaled(x):
+    """``(tensor, scale or None)`` of what a norm returned."""
+    return (x.tensor, x.scale) if isinstance(x, ScaledRows) else (x, None)
+
+
 class ResidualStream:
     """The float residual stream ``[T, H]`` with at most one sublayer output not yet added.
 
     A sublayer's output is recorded with :meth:`add`; the next norm folds it into
-    the stream while it normalises (one pass over memory instead of two).
+    the stream while it normalises (one pass over memory instead of two).  Where a
+    sublayer ends in a product and the kernels can do it, :meth:`add_linear` goes further:
+    the product's epilogue adds into the stream and prepares the next norm's output, which
+    then waits in ``ready`` for that norm (``ready_for``).
     """
 
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.ready: Optional[ScaledRows] = None
+        self.ready_for = None
 
     def add(self, delta: torch.Tensor) -> None:
         if self.pending is not None:
             self.flush()
         self.pending = delta
+        self.ready = self.ready_for = None
+
+    def add_linear(self, d: DeferredLinear, norm=None, consumer=None) -> None:
+        """Add ``d.x @ d.w^T``.  ``norm`` is the norm that reads the stream next and
+        ``consumer`` the part that takes its output; the fused path needs a norm with a
+        ``fused_scale`` (weight, eps) over whole rows and a consumer that accepts
+        :class:`ScaledRows`."""
+        from .linear import linear_add_norm
+        fs = getattr(norm, "fused_scale", None)
+        if fs is not None and getattr(consumer, "accepts_scaled_rows", False):
+            self.flush()
+            weight, eps = fs()
+            got = linear_add_norm(d.x, d.w, self.x, weight, eps)
+            if got is not None:
+                self.ready, self.ready_for = ScaledRows(*got), norm
+                return
+        self.add(d.compute())
 
     def flush(self) -> None:
         if self.pending is not None:

@@ -9,7 +9,7 @@ from __future__ import annotations
 from typing import List
 
 from ..config.specs import LayerSpec, NameLayout
-from .base import (BuildEnv, EntryView, Part, ResidualStream, StepContext, build_ffn,
+from .base import (BuildEnv, EntryView, Part, ResidualStream, ScaledRows, StepContext, build_ffn,
                    build_mixer, build_norm, register_block)
 
 
@@ -34,9 +34,31 @@ class PreNormBlock(Part):
         for part in self.parts():
             part.load(get)
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, view: EntryView) -> None:
-        stream.add(self.mixer.forward(self.input_norm.forward(stream), ctx, view))
-        stream.add(self.ffn.forward(self.post_norm.forward(stream), ctx))
+    def forward(self, stream: ResidualStream, ctx: StepContext, view: EntryView,
+                successor: "PreNormBlock" = None) -> None:
+        """``successor``: the block that runs next on this stream, if any; its input norm
+        can then be prepared by this block's last product."""
+        h = self._for(self.mixer, self.input_norm.forward(stream))
+        deferred = getattr(self.mixer, "forward_deferred", None)
+        if deferred is not None:
+            stream.add_linear(deferred(h, ctx, view), self.post_norm, self.ffn)
+        else:
+            stream.add(self.mixer.forward(h, ctx, view))
+        h = self._for(self.ffn, self.post_norm.forward(stream))
+        deferred = getattr(self.ffn, "forward_deferred", None)
+        if deferred is not None:
+            nxt = successor if isinstance(successor, PreNormBlock) else None
+            stream.add_linear(deferred(h, ctx), nxt.input_norm if nxt else None,
+                              nxt.mixer if nxt else None)
+        else:
+            stream.add(self.ffn.forward(h, ctx))
+
+    @staticmethod
+    def _for(part, h):
+        """``h`` as ``part`` can take it."""
+        if isinstance(h, ScaledRows) and not getattr(part, "accepts_scaled_rows", False):
+            return h.dense()
+        return h
 
 
 register_block("prenorm", PreNormBlock)

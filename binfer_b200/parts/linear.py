@@ -96,3 +96,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     if prof is not None:
         prof.end("cublas_gemm_bf16")
     return out
+
+
+FUSE_NORM = os.environ.get("BINFER_B200_FUSE_NORM", "1") != "0"
+
+
+def linear_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
+                    norm_w: torch.Tensor, eps: float):
+    """``resid += x @ w^T`` with the next RMSNorm prepared in the same kernel: returns
+    ``(bfloat16(resid * norm_w), ops.RowScale)``, the norm's output short of the factor
+    ``rsqrt(mean(resid^2) + eps)`` per row, or None, having done nothing, where the cluster
+    kernel does not run (float32, more than 16 tokens, shapes without a plan)."""
+    M, (N, K) = x.shape[0], w.shape
+    if (not FUSE_NORM or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+            or not _use_cluster(M, N, K)):
+        return None
+    plan = _plans.get((N, K))
+    if plan is None:
+        plan = _plans[(N, K)] = ops.gemm_cluster_plan(N, K, x.device) or False
+    if not plan:
+        return None
+    return ops.gemm_bf16_cluster_add_norm(x, w, resid, norm_w, eps, ops.error_word(x.device),
+                                          *plan)

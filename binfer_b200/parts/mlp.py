@@ -14,7 +14,8 @@ import torch
 from ..config.specs import GatedMLPSpec
 from ..csrc import ops
 from ..weights.loader import ParamSpec
-from .base import BuildEnv, FeedForward, StepContext, register_ffn
+from .base import (BuildEnv, DeferredLinear, FeedForward, ScaledRows, StepContext, register_ffn,
+                   split_scaled)
 from .linear import linear
 
 
@@ -39,11 +40,20 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([get(g), get(u)], dim=0).contiguous()
         self.w_down = get(d)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    accepts_scaled_rows = True
+
+    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+        return self.forward_deferred(x, ctx).compute()
+
+    def forward_deferred(self, x, ctx: StepContext) -> DeferredLinear:
+        """Everything but the down projection (see ``GQAAttention.forward_deferred``)."""
+        if isinstance(x, ScaledRows) and (self.inter % 8 or self.inter < 256):
+            x = x.dense()                  # the activation kernel takes the factor at other sizes only
+        x, row_scale = split_scaled(x)
         gu = linear(x, self.w_gate_up)
         h = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gu, h)
-        return linear(h, self.w_down)
+        ops.silu_mul(gu, h, row_scale=row_scale)
+        return DeferredLinear(h, self.w_down)
 
 
 register_ffn("gated_mlp", GatedMLP)

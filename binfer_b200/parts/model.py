@@ -118,9 +118,11 @@ class DecoderModel:
         resid = torch.empty((ctx.T, spec.hidden_size), dtype=torch.float32, device=self.env.device)
         ops.embed_gather(self.embed, ctx.token_ids, resid, spec.embedding_scale, ctx.err)
         stream = ResidualStream(resid)
+        last = len(spec.schedule) - 1
         for e, entry in enumerate(spec.schedule):
             ctx.entry = e
-            self.blocks[entry.layer].forward(stream, ctx, views[e])
+            nxt = self.blocks[spec.schedule[e + 1].layer] if e < last else None
+            self.blocks[entry.layer].forward(stream, ctx, views[e], nxt)
         R = ctx.logit_rows.shape[0]
         if R == 0:
             stream.flush()

@@ -34,7 +34,12 @@ class RMSNorm(Norm):
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
                 n_rows: int = 0) -> torch.Tensor:
         """Normed activations of every row, or of ``rows`` only (the stream is then
-        left as it is: nothing reads it afterwards)."""
+        left as it is: nothing reads it afterwards).  May return ``ScaledRows`` when the
+        stream holds this norm's output already (``ResidualStream.add_linear``)."""
+        if rows is None and stream.ready_for is self:
+            out, stream.ready, stream.ready_for = stream.ready, None, None
+            return out           # ScaledRows: the product before already prepared this norm
+        stream.ready = stream.ready_for = None
         n = n_rows if rows is not None else stream.x.shape[0]
         out = torch.empty((n, self.size), dtype=self.env.dtype, device=self.env.device)
         ops.add_rmsnorm(stream.x, stream.pending, self.weight, out, self.eps, rows=rows,
@@ -42,6 +47,11 @@ class RMSNorm(Norm):
         if rows is None:
             stream.pending = None
         return out
+
+
+    def fused_scale(self):
+        """(weight, eps): what a product needs to prepare this norm in its epilogue."""
+        return self.weight, self.eps
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -38,7 +38,17 @@ TINY_M = dict(
     use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
     attention_bias=False)
 
+# wide enough (2048 inputs to the output and down projections) for the decode step's
+# split-K cluster products, and with them the products that prepare the next norm
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=3, hidden_size=1024,
+    num_attention_heads=16, num_key_value_heads=4, head_dim=128, intermediate_size=2048,
+    vocab_size=600, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
+    attention_bias=False)
+
 TINY = {
+    "F": dict(raw=TINY_F, std=0.03, norm_std=0.05, page_size=64, seed=55),
     "M": dict(raw=TINY_M, std=0.05, norm_std=0.02, page_size=16, seed=44),
     "A": dict(raw=TINY_A, std=0.02, norm_std=0.01, page_size=16, seed=11),
     "B": dict(raw=TINY_B, std=0.05, norm_std=0.05, page_size=8, seed=22),

@@ -284,6 +284,40 @@ def test_decode_attention_more_splits_than_one_merge_pass(cuda_device, variant):
     _close(out, ref, BF16)
 
 
+@pytest.mark.parametrize("M,N,K,bn,c", [(8, 4096, 4096, 128, 4), (3, 200, 512, 64, 2),
+                                        (16, 1000, 320, 80, 1)])
+def test_gemm_cluster_adds_into_the_stream_and_prepares_the_norm(cuda_device, M, N, K, bn, c):
+    """resid += x w^T in float; xt = bf16(resid * norm_w); the partial sums of squares add up
+    to the rows' sums, so that xt times the factor is the RMSNorm of the new stream."""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(M, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(BF16).to(cuda_device)
+    resid0 = (3.0 * torch.randn(M, N, generator=g)).to(cuda_device)
+    nw = (1.0 + 0.1 * torch.randn(N, generator=g)).to(cuda_device)
+    eps = 1e-5
+    resid = resid0.clone()
+    err = ops.error_word(cuda_device)
+    got = ops.gemm_bf16_cluster_add_norm(x, w, resid, nw, eps, err, bn, c)
+    assert got is not None and int(err.item()) == 0
+    xt, scale = got
+    want = resid0.double().cpu() + x.double().cpu() @ w.double().cpu().T
+    assert float((resid.double().cpu() - want).abs().max()) <= 4e-7 * math.sqrt(K) * float(want.abs().max())
+    assert scale.partials.shape == (M, -(-N // bn) * c) and scale.width == N
+    ss = scale.partials.double().sum(1).cpu()
+    assert torch.allclose(ss, (want ** 2).sum(1), rtol=1e-5)
+    normed = want * torch.rsqrt((want ** 2).mean(1, keepdim=True) + eps) * nw.double().cpu()
+    _close(xt.float() * scale.factors().unsqueeze(1), normed, BF16)
+    # the factor applied by the kernels that come after the next product
+    I = 264
+    gu = torch.randn(M, 2 * I, generator=g).to(BF16).to(cuda_device)
+    out = torch.empty(M, I, device=cuda_device, dtype=BF16)
+    ops.silu_mul(gu, out, row_scale=scale)
+    f = scale.factors().double().cpu().unsqueeze(1)
+    gd = gu.double().cpu() * f
+    _close(out, gd[:, :I] / (1 + torch.exp(-gd[:, :I])) * gd[:, I:], BF16)
+
+
 # ------------------------------------------------------------------------ sampling
 def _sample(dev, logits, temperature, top_k=0, top_p=1.0, u=0.0):
     from binfer_b200.csrc import ops

@@ -18,7 +18,7 @@ TOL = {torch.float32: 2e-5, torch.bfloat16: 3e-2}
 TOL_RMS = {torch.float32: 5e-6, torch.bfloat16: 1e-2}
 
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 70], "W": [3, 30, 64, 101],
-           "M": [2, 45, 150, 333]}
+           "M": [2, 45, 150, 333], "F": [3, 40, 70, 130]}
 
 
 def _requests(which, extra=()):
@@ -141,3 +141,48 @@ def test_replay_through_captured_decode_steps(cuda_device, plain_logits, dtype):
         got = H.run_trace(runner, steps)
         assert getattr(runner, "graph_replays", 0) > 0
         _compare(got, ref, dtype, f"{which}/graphs/{make.__name__}")
+
+
+class _Names:
+    """A profiler stand-in that only records which kernels were launched."""
+    def __init__(self):
+        self.names = set()
+
+    def begin(self, name):
+        self.names.add(name)
+
+    def end(self, name):
+        pass
+
+
+@pytest.mark.parametrize("regime", ["tail", "mixed"])
+def test_replay_with_products_that_prepare_the_next_norm(cuda_device, plain_logits, regime):
+    """A model wide enough for the decode step's cluster products: steps of few tokens run
+    the output and down projections with the add into the stream and the next norm in their
+    epilogue, and the norm's factor is applied after the next product.  Same logits as the
+    plain implementation, and (to bfloat16 rounding) as the same steps without the fusion."""
+    from binfer_b200.csrc import ops
+    import importlib
+    lin = importlib.import_module("binfer_b200.parts.linear")
+    which, dtype = "F", torch.bfloat16
+    reqs = _requests(which, (55, 61) if regime == "mixed" else ())
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    steps = {"tail": H.trace_decode_tail, "mixed": H.trace_mixed}[regime](reqs)
+    ps = H.TINY[which]["page_size"]
+    outs = []
+    for fuse in (True, False):
+        lin.FUSE_NORM = fuse
+        seen = _Names()
+        ops.set_profiler(seen)
+        try:
+            got = H.run_trace(_runner(model_dir, dtype, ps, H.peak_pages(steps, ps)), steps)
+        finally:
+            ops.set_profiler(None)
+            lin.FUSE_NORM = True
+        assert ("gemm_bf16_cluster_add_norm" in seen.names) == fuse
+        if fuse:
+            assert "silu_mul_scaled" in seen.names
+        _compare(got, ref, dtype, f"{which}/{regime}/fused={fuse}")
+        outs.append(got)
+    worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
+    assert worst <= TOL[dtype], f"fused and unfused steps differ by {worst:.3g}"
