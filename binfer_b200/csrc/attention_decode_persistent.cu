@@ -28,6 +28,7 @@
 // BF_ERR_WAIT, its group leaves together, and the others run into their own limits.
 // No copy uses multicast.
 #include <float.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "mma_utils.cuh"
@@ -144,7 +145,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
                                    float* __restrict__ part_o, float* __restrict__ part_ml,
                                    int n_rows, int nh, int nkv, int page_size, int num_pages,
                                    int window, int max_splits, float scale_log2, int slots,
-                                   int groups, int* __restrict__ err) {
+                                   int groups, int early, int* __restrict__ err) {
   constexpr int HALVES = D / 64;
   constexpr int HALF_ELEMS = DP_SPLIT * 64;
   constexpr int TILE_ELEMS = DP_SPLIT * D;
@@ -180,7 +181,10 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  bf_pdl_wait();
+  // What follows reads the step's description (rows, positions, block tables) and, in the
+  // producer, cache pages of keys that earlier steps wrote: none of it comes from the kernel
+  // before this one, which writes this step's queries and this step's keys and values.  So it
+  // runs ahead of the wait; only the queries and the splits that hold a row's newest key wait.
   if (warp == 0) {
     // items before each row: (splits the row's keys touch) x (kv heads), in row order
     int running = 0;
@@ -212,6 +216,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
   __syncthreads();
   const int total = row_start[n_rows];
   const int pages = DP_SPLIT / page_size;
+  if (warp != 0) bf_pdl_wait();                          // the producer waits further down
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -224,6 +229,26 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
                            page_size, num_pages, window, table_stride, row_start, row_t, row_p,
                            row_seq, block_tables, err);
     bool failed = false;
+    bool waited = false;
+    if (!early) bf_pdl_wait(), waited = true;
+    // the queries of the items issued before the wait are fetched right after it
+    auto wait_then_queries = [&]() {
+      bf_pdl_wait();
+      waited = true;
+      if (lane == 0)
+        for (int e = 0; e < groups * qsg; ++e) {
+          int* inf = info + e * 8;
+          if (inf[7]) {
+            inf[7] = 0;
+            dp_bulk_load(qbuf + (size_t)e * G * D,
+                         q + ((size_t)inf[5] * nh + (size_t)inf[1] * G) * D,
+                         (uint32_t)(G * D * 2), full + inf[6]);
+          }
+        }
+      __syncwarp();
+    };
+    if (lane < groups * qsg) info[lane * 8 + 7] = 0;
+    __syncwarp();
     for (int it0 = 0; !failed && blockIdx.x + it0 * gridDim.x < total; it0 += nb) {
       const DpItem cur = nxt;
       nxt = dp_lookup(blockIdx.x + (it0 + nb + sub) * gridDim.x, sub < nb, pg, total, n_rows, nkv,
@@ -240,6 +265,9 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
         const int pgrp = it % groups, k = it / groups;
         const int qi = pgrp * qsg + k % qsg;
         bool ok = true;
+        // ahead of the wait: tiles of keys that earlier steps wrote, into slots never used
+        if (!waited && ((2 * k + 1) / spg > 0 || split == row_p[r] / DP_SPLIT))
+          wait_then_queries();
         {
           const int n = 2 * k, slot = pgrp * spg + n % spg, use = n / spg;
           if (use > 0) ok = bf_mbar_wait_bounded(empty + slot, (use - 1) & 1);
@@ -252,8 +280,12 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
             int* inf = info + qi * 8;
             inf[0] = r; inf[1] = g; inf[2] = split;
             bf_mbar_expect_tx(full + slot, TILE_BYTES + (uint32_t)(G * D * 2));
-            dp_bulk_load(qbuf + (size_t)qi * G * D, q + ((size_t)t * nh + (size_t)g * G) * D,
-                         (uint32_t)(G * D * 2), full + slot);
+            if (waited) {
+              dp_bulk_load(qbuf + (size_t)qi * G * D, q + ((size_t)t * nh + (size_t)g * G) * D,
+                           (uint32_t)(G * D * 2), full + slot);
+            } else {
+              inf[5] = t; inf[6] = slot; inf[7] = 1;
+            }
           }
           __syncwarp();
           if (lane < pages) {
@@ -281,6 +313,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
         }
       }
     }
+    if (!waited) wait_then_queries();
     if (failed && lane == 0) atomicOr(err, BF_ERR_WAIT);
     return;
   }
@@ -494,7 +527,9 @@ static int launch_persistent(const void* q, const void* k_cache, const void* v_c
   return bf_launch_pdl(kern, dim3(grid), dim3(DP_THREADS), smem, stream, mk, mv,
                        (const __nv_bfloat16*)q, rows, seq_of_token, positions, block_tables,
                        table_stride, part_o, part_ml, n_rows, nh, nkv, page_size, num_pages,
-                       window, max_splits, scale * 1.4426950408889634f, slots, groups, err);
+                       window, max_splits, scale * 1.4426950408889634f, slots, groups,
+                       getenv("BINFER_B200_ATTN_EARLY") ? atoi(getenv("BINFER_B200_ATTN_EARLY")) : 1,
+                       err);
 }
 
 // Same arguments and result as bf_decode_attention.  Returns cudaErrorInvalidValue for what

@@ -78,10 +78,12 @@ __global__ void qk_norm_rope_kv_write_kernel(
   for (int i = lane; i < d; i += 32) bf_st(dst + i, x[i]);
 }
 
-// The common case in registers: bf16, head size 128, full rotation (64 pairs).  A block per
-// token: the 64 sines and cosines of the token's position are computed once and shared by
-// all its heads; each warp then walks heads, lane l holding elements 4l..4l+3, whose
-// rotation partners sit in lane l ^ 16.
+// The common case in registers: bf16, head size 128, full rotation (64 pairs).  A block takes
+// some of a token's heads (blockIdx.y; all of them when there are many tokens): the 64 sines
+// and cosines of the token's position are computed once per block and shared by its heads;
+// each warp then walks its heads, lane l holding elements 4l..4l+3, whose rotation partners
+// sit in lane l ^ 16.  With few tokens every warp has one head: the kernel is then two
+// dependent round trips long (position, then the head's values) instead of one per head.
 __global__ void qk_norm_rope_kv_write_d128_kernel(
     const __nv_bfloat16* __restrict__ qkv, long long row_stride, const float* __restrict__ q_w,
     const float* __restrict__ k_w, const float* __restrict__ inv_freq,
@@ -96,6 +98,13 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x;
   const BfRowShare share = bf_row_fetch(rs, t, lane);    // in flight under the sines and cosines
+  const int slot = k_cache ? slots[t] : -1;
+  // so are the values of the warp's first head
+  const int hh_first = blockIdx.y * warps + warp;
+  uint2 raw_first = make_uint2(0u, 0u);
+  if (hh_first < nh + 2 * nkv)
+    raw_first = *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride +
+                                                (size_t)hh_first * D + lane * 4);
   if (threadIdx.x < 64) {
     float sn, cs;
     sincosf((float)positions[t] * inv_freq[threadIdx.x], &sn, &cs);
@@ -104,16 +113,17 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
   }
   __syncthreads();
   const float row_factor = bf_row_finish(rs, share);
-  const int slot = k_cache ? slots[t] : -1;
   const bool upper = lane >= 16;               // holds elements i + 64 of the pairs
   const int fi = (lane & 15) * 4;
   const float4 wq = q_w ? *reinterpret_cast<const float4*>(q_w + lane * 4) : make_float4(1, 1, 1, 1);
   const float4 wk = k_w ? *reinterpret_cast<const float4*>(k_w + lane * 4) : make_float4(1, 1, 1, 1);
-  for (int hh = warp; hh < nh + 2 * nkv; hh += warps) {
+  for (int hh = hh_first; hh < nh + 2 * nkv; hh += gridDim.y * warps) {
     const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
     if (!is_q && slot < 0) continue;
-    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride +
-                                                      (size_t)hh * D + lane * 4);
+    const uint2 raw = hh == hh_first
+                          ? raw_first
+                          : *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride +
+                                                            (size_t)hh * D + lane * 4);
     const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
     const float2 a = __bfloat1622float2(r2[0]), b = __bfloat1622float2(r2[1]);
     float x[4] = {a.x * row_factor, a.y * row_factor, b.x * row_factor, b.y * row_factor};
@@ -173,8 +183,11 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
       ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_cache & 7) == 0 &&
       ((uintptr_t)v_cache & 7) == 0 && ((uintptr_t)inv_freq & 15) == 0 &&
       ((uintptr_t)q_w & 15) == 0 && ((uintptr_t)k_w & 15) == 0) {
-    return bf_launch_pdl(qk_norm_rope_kv_write_d128_kernel, dim3(T),
-                         dim3(total >= 16 ? 256 : 128), 0, stream, (const __nv_bfloat16*)qkv,
+    const int block = total >= 16 ? 256 : 128;
+    // few tokens: a warp per head; many: a block per token, which walks the heads
+    const int parts = T <= 64 ? (total * 32 + block - 1) / block : 1;
+    return bf_launch_pdl(qk_norm_rope_kv_write_d128_kernel, dim3(T, parts), dim3(block), 0,
+                         stream, (const __nv_bfloat16*)qkv,
                          row_stride, q_w, k_w, inv_freq, positions, slots, (__nv_bfloat16*)q_out,
                          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, page_size,
                          num_slots, eps, rs, err);
