@@ -245,8 +245,10 @@ decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
                               int max_splits) {
   __shared__ float wgt[MERGE_PASS];
   __shared__ float red[4];
+  BF_TRACE_POINT(10 * BF_TR_MERGE);
   bf_pdl_trigger();
   bf_pdl_wait();
+  BF_TRACE_POINT(10 * BF_TR_MERGE + 1);
   const int r = blockIdx.x, h = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const size_t base = ((size_t)r * nh + h) * max_splits;
@@ -457,3 +459,5 @@ BF_EXPORT int bf_decode_attention_static(const void* q, const void* k_cache, con
                              table_stride, out, part_o, part_ml, n_rows, nh, nkv, d, page_size,
                              num_pages, window, max_splits, scale, err, stream);
 }
+
+BF_TRACE_READER(bf_trace_read_attention_decode)

@@ -173,6 +173,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+  BF_TRACE_POINT(10 * BF_TR_ATTN);
   bf_pdl_trigger();
   if (tid == 32) {
     for (int s = 0; s < slots; ++s) {
@@ -234,6 +235,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
     // the queries of the items issued before the wait are fetched right after it
     auto wait_then_queries = [&]() {
       bf_pdl_wait();
+      BF_TRACE_POINT(10 * BF_TR_ATTN + 1);
       waited = true;
       if (lane == 0)
         for (int e = 0; e < groups * qsg; ++e) {
@@ -315,6 +317,7 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
     }
     if (!waited) wait_then_queries();
     if (failed && lane == 0) atomicOr(err, BF_ERR_WAIT);
+    BF_TRACE_POINT(10 * BF_TR_ATTN + 2);                 // the producer's end: all tiles requested
     return;
   }
 
@@ -566,3 +569,5 @@ BF_EXPORT int bf_decode_attention_persistent(const void* q, const void* k_cache,
   return bf_decode_attention_merge(part_o, part_ml, rows, positions, out, n_rows, nh, d, window,
                                    max_splits, stream);
 }
+
+BF_TRACE_READER(bf_trace_read_attention_decode_persistent)

@@ -27,6 +27,13 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 
+# BINFER_B200_TRACE=1: the kernels of the decode step record timestamps (common.cuh, BF_TRACE);
+# that library is a build of its own in a folder of its own.
+TRACE = os.environ.get("BINFER_B200_TRACE", "0") == "1"
+if TRACE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DBF_TRACE"]
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -67,7 +74,7 @@ def build_dir() -> str:
     if override:
         os.makedirs(override, exist_ok=True)
         return override
-    local = os.path.join(HERE, "_build")
+    local = os.path.join(HERE, "_build_trace" if TRACE else "_build")
     try:
         os.makedirs(local, exist_ok=True)
         probe = os.path.join(local, f".w{os.getpid()}")
@@ -76,7 +83,8 @@ def build_dir() -> str:
         os.remove(probe)
         return local
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"binfer_b200_build_{os.getuid()}")
+        d = os.path.join(tempfile.gettempdir(),
+                         f"binfer_b200_build{'_trace' if TRACE else ''}_{os.getuid()}")
         os.makedirs(d, exist_ok=True)
         return d
 

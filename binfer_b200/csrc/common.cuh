@@ -128,3 +128,48 @@ __device__ __forceinline__ float bf_row_finish(const BfRowScale& rs, const BfRow
 __device__ __forceinline__ float bf_row_factor(const BfRowScale& rs, int row, int lane) {
   return bf_row_finish(rs, bf_row_fetch(rs, row, lane));
 }
+
+// ------------------------------------------------------------------- timeline of a step
+// Built with -DBF_TRACE (BINFER_B200_TRACE=1 in the environment when the library is
+// compiled; it goes to a build folder of its own), the decode step's kernels record the
+// global timer when block 0 starts, when its dependency wait returns and when it ends.  Each
+// source file keeps its own list and exports a reader; `python -m binfer_b200.microbench
+// step_timeline` puts them in order.  Without the flag the macros are empty.
+#ifdef BF_TRACE
+#define BF_TRACE_EVENTS 8192
+static __device__ unsigned long long bf_trace_time[BF_TRACE_EVENTS];
+static __device__ int bf_trace_code[BF_TRACE_EVENTS];
+static __device__ int bf_trace_count;
+__device__ __forceinline__ void bf_trace_point(int code) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    const int i = atomicAdd(&bf_trace_count, 1);
+    if (i < BF_TRACE_EVENTS) {
+      bf_trace_time[i] = t;
+      bf_trace_code[i] = code;
+    }
+  }
+}
+#define BF_TRACE_POINT(code) bf_trace_point(code)
+// Copies this file's events out (times in ns, codes), empties the list, returns their number.
+#define BF_TRACE_READER(name)                                                    \
+  BF_EXPORT int name(unsigned long long* times, int* codes) {                    \
+    int n = 0, zero = 0;                                                         \
+    cudaMemcpyFromSymbol(&n, bf_trace_count, sizeof(int));                       \
+    cudaMemcpyFromSymbol(times, bf_trace_time, sizeof(bf_trace_time));           \
+    cudaMemcpyFromSymbol(codes, bf_trace_code, sizeof(bf_trace_code));           \
+    cudaMemcpyToSymbol(bf_trace_count, &zero, sizeof(int));                      \
+    return n < BF_TRACE_EVENTS ? n : BF_TRACE_EVENTS;                            \
+  }
+#else
+#define BF_TRACE_POINT(code)
+#define BF_TRACE_READER(name)
+#endif
+// kernel ids of the trace codes (code = 10 * id + phase; phase 0 start, 1 after the wait, 2 end)
+#define BF_TR_RMSNORM 1
+#define BF_TR_SILU 2
+#define BF_TR_QKNORM 3
+#define BF_TR_ATTN 4
+#define BF_TR_MERGE 5
+#define BF_TR_GEMM 6

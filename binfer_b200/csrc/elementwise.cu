@@ -95,8 +95,10 @@ __global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid,
                                             const int* __restrict__ rows, int H, float eps,
                                             int write_back) {
   __shared__ float scratch[33];
+  BF_TRACE_POINT(10 * BF_TR_RMSNORM);
   bf_pdl_trigger();
   bf_pdl_wait();
+  BF_TRACE_POINT(10 * BF_TR_RMSNORM + 1);
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * H;
@@ -234,8 +236,10 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
 __global__ void silu_mul_bf16_scaled_kernel(const __nv_bfloat16* __restrict__ gu,
                                             __nv_bfloat16* __restrict__ out, int T, int I,
                                             BfRowScale rs) {
+  BF_TRACE_POINT(10 * BF_TR_SILU);
   bf_pdl_trigger();
   bf_pdl_wait();
+  BF_TRACE_POINT(10 * BF_TR_SILU + 1);
   const int lane = threadIdx.x & 31;
   const int per_row = I / 8;
   const size_t n = (size_t)T * per_row;
@@ -277,8 +281,10 @@ __global__ void silu_mul_bf16_scaled_kernel(const __nv_bfloat16* __restrict__ gu
 // bf16, I a multiple of 8: eight elements per thread with 16-byte loads and stores.
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
                                          __nv_bfloat16* __restrict__ out, int T, int I) {
+  BF_TRACE_POINT(10 * BF_TR_SILU);
   bf_pdl_trigger();
   bf_pdl_wait();
+  BF_TRACE_POINT(10 * BF_TR_SILU + 1);
   const int per_row = I / 8;
   const size_t n = (size_t)T * per_row;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -355,3 +361,5 @@ BF_EXPORT int bf_copy_ids(int* dst, const int* src, const int* pairs, int n, cud
   copy_ids_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, src, pairs, n);
   return bf_launch_status();
 }
+
+BF_TRACE_READER(bf_trace_read_elementwise)

@@ -79,6 +79,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                     const ClusterGemmParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  BF_TRACE_POINT(10 * BF_TR_GEMM);
   bf_pdl_trigger();
   uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(base);
@@ -136,6 +137,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     }
   }
   bf_pdl_wait();
+  BF_TRACE_POINT(10 * BF_TR_GEMM + 1);
 
   if (warp == 2) {
     if (lane == 0) {
@@ -263,6 +265,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   }
 
   __syncthreads();
+  BF_TRACE_POINT(10 * BF_TR_GEMM + 2);
   if (*abort && threadIdx.x == 0) atomicOr(p.err, BF_ERR_WAIT);
   if (warp == 1) {
     tc_fence_after();
@@ -425,3 +428,5 @@ BF_EXPORT int bf_gemm_bf16_cluster_add_norm(const void* x, const void* w, int to
   if (n_partials) *n_partials = ((features + bn - 1) / bn) * cluster;
   return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
 }
+
+BF_TRACE_READER(bf_trace_read_gemm_tcgen05_cluster)

@@ -93,8 +93,10 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
     float eps, BfRowScale rs, int* __restrict__ err) {
   constexpr int D = 128;
   __shared__ float sn_s[64], cs_s[64];
+  BF_TRACE_POINT(10 * BF_TR_QKNORM);
   bf_pdl_trigger();
   bf_pdl_wait();
+  BF_TRACE_POINT(10 * BF_TR_QKNORM + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x;
   const BfRowShare share = bf_row_fetch(rs, t, lane);    // in flight under the sines and cosines
@@ -206,3 +208,5 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
         page_size, num_slots, eps, rs, err);
   return bf_launch_status();
 }
+
+BF_TRACE_READER(bf_trace_read_qkv_post)

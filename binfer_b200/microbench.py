@@ -4,6 +4,7 @@
     python -m binfer_b200.microbench prefill_attention --tokens 2048
     python -m binfer_b200.microbench gemm --tokens 8 --features 6144 --k 4096 [--library]
     python -m binfer_b200.microbench add_rmsnorm --tokens 8 --hidden 4096
+    BINFER_B200_TRACE=1 python -m binfer_b200.microbench step_timeline --batch 8 --ctx 4096 --layers 6
 
 Sizes default to the Qwen3-8B shape.  Each kernel runs on a rotation of input sets
 larger than the L2 cache, after warm-up, between CUDA events; the line printed gives
@@ -12,6 +13,13 @@ fraction of the measured peak (``MEASURED_PEAKS.json`` beside the package, else 
 stated fallback).  The reference measures its own peaks the same way at run time
 (src/profiler/profiler.ts:553-659).  ``--iters 1 --warmup 0`` gives a run small
 enough to put under a profiler.
+
+``step_timeline`` runs whole decode steps of a random-weight model of the given layer sizes
+(CUDA graphs, as in serving) with the library built for tracing (``BINFER_B200_TRACE=1``
+must be set before the first import: the kernels of the step then record the GPU's global
+timer when their first block starts, when its dependency wait returns and when it ends)
+and prints the last step's events in order, with the time since the previous one.  Library
+products are not instrumented; they show as the gaps around the engine's own kernels.
 """
 from __future__ import annotations
 
@@ -165,11 +173,76 @@ def add_rmsnorm(a):
     report("add_rmsnorm", us, nbytes=T * H * (4 + 4 + 2 + 2), tokens=T, hidden=H)
 
 
+def step_timeline(a):
+    import ctypes
+    from . import Engine
+    from .config import Qwen3Config
+    from .engine.runner import StepItem
+    from .sampling import SamplingParams
+    from .csrc import build
+    if not build.TRACE:
+        raise SystemExit("step_timeline: set BINFER_B200_TRACE=1 in the environment")
+    dev = torch.device("cuda:0")
+    B, ctx = a.batch, a.ctx
+    raw = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=a.layers,
+               hidden_size=a.hidden, num_attention_heads=a.heads, num_key_value_heads=a.kv_heads,
+               head_dim=a.head_dim, intermediate_size=a.intermediate, vocab_size=a.vocab,
+               rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+               max_position_embeddings=max(ctx, 4096), hidden_act="silu", attention_bias=False,
+               use_sliding_window=False)
+    cfg = Qwen3Config.from_dict(raw)
+    ps = a.page_size
+    eng = Engine(cfg, "bfloat16", random_seed=0, num_pages=B * (-(-ctx // ps)) + 64, page_size=ps,
+                 max_seq_len=ctx, max_batch_size=B, max_tokens_per_step=2048, cuda_graphs=True)
+    runner, sampler = eng.runner, eng.sampler
+    gen = torch.Generator().manual_seed(0)
+    steps = 8
+    rids = []
+    for i in range(B):
+        rid = f"t{i}"
+        runner.add_request(rid)
+        toks = torch.randint(0, cfg.vocab_size, (ctx - steps - 1,), generator=gen).tolist()
+        for s0 in range(0, len(toks), 2048):
+            runner.step([StepItem(rid, toks[s0:s0 + 2048], [])])
+        rids.append(rid)
+    params = [SamplingParams(temperature=0.0, seed=0) for _ in rids]
+    torch.cuda.synchronize()
+    readers = [getattr(ops.lib(), "bf_trace_read_" + f) for f in
+               ("elementwise", "qkv_post", "attention_decode_persistent", "attention_decode",
+                "gemm_tcgen05_cluster")]
+    times = (ctypes.c_ulonglong * 8192)()
+    codes = (ctypes.c_int * 8192)()
+    events = []
+    for i in range(steps):
+        if i == steps - 1:
+            torch.cuda.synchronize()
+            for rd in readers:
+                rd(times, codes)                         # empty the lists: only the last step stays
+        logits = runner.step([StepItem(r, [int(torch.randint(0, cfg.vocab_size, (1,), generator=gen))],
+                                       [0]) for r in rids])
+        sampler.sample_async(logits, params, [0] * B, [[]] * B)
+    torch.cuda.synchronize()
+    for rd in readers:
+        n = rd(times, codes)
+        events += [(times[i], codes[i]) for i in range(n)]
+    events.sort()
+    names = {1: "add_rmsnorm", 2: "silu_mul", 3: "qk_norm_rope", 4: "decode_attention",
+             5: "attention_merge", 6: "gemm_cluster"}
+    phases = ["first block starts", "wait returns", "ends"]
+    t0 = prev = events[0][0]
+    print(f"# decode step, batch {B}, context {ctx}, {a.layers} layers; microseconds", flush=True)
+    for t, c in events:
+        print(f"{(t - t0) / 1e3:10.2f} {(t - prev) / 1e3:8.2f}  {names.get(c // 10, '?'):18s} {phases[c % 10]}")
+        prev = t
+    print(json.dumps({"kernel": "step_timeline", "us": round((events[-1][0] - t0) / 1e3, 2),
+                      "events": len(events), "batch": B, "ctx": ctx, "layers": a.layers}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m binfer_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["decode_attention", "prefill_attention", "gemm",
-                                       "add_rmsnorm"])
+                                       "add_rmsnorm", "step_timeline"])
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
@@ -181,6 +254,9 @@ def main(argv=None):
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=6, help="step_timeline: layers of the model")
+    ap.add_argument("--intermediate", type=int, default=12288)
+    ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--features", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0, help="feature rows per tile (0: chosen)")
@@ -199,7 +275,7 @@ def main(argv=None):
     global GRAPH
     GRAPH = not a.no_graph
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention,
-     "gemm": gemm, "add_rmsnorm": add_rmsnorm}[a.kernel](a)
+     "gemm": gemm, "add_rmsnorm": add_rmsnorm, "step_timeline": step_timeline}[a.kernel](a)
     return 0
 
 
