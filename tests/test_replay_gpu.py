@@ -126,11 +126,12 @@ def test_first_tokens(cuda_device, plain_logits):
         _compare(H.run_trace(runner, steps), ref, torch.float32, f"{which}/first tokens")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-def test_replay_through_captured_decode_steps(cuda_device, plain_logits, dtype):
+@pytest.mark.parametrize("which,dtype", [("M", torch.float32), ("M", torch.bfloat16),
+                                         ("F", torch.bfloat16)], ids=["M-f32", "M-bf16", "F-bf16"])
+def test_replay_through_captured_decode_steps(cuda_device, plain_logits, which, dtype):
     """Steps of single tokens replayed from CUDA graphs (padded to a bucket, block tables of
-    full width) give what eager steps give."""
-    which = "M"
+    full width) give what eager steps give.  (F: with the products that prepare the next
+    norm, the cluster kernels and their dependent launches inside the graph.)"""
     reqs = _requests(which, (55, 61))
     model_dir, ref = plain_logits(which, dtype, reqs)
     ps = H.TINY[which]["page_size"]
