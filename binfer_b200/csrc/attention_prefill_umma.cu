@@ -48,53 +48,6 @@ constexpr int AU_THREADS = 320;   // eight softmax warps, the TMA warp, the MMA 
 constexpr int AU_TMA_WARP = 8;
 constexpr int AU_MMA_WARP = 9;
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
-          taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-      "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
-      "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
-      "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-// 2^x by the special-function unit (x <= 0 here; -inf gives 0)
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// MN-major operand (rows = K index, 64 contiguous elements of the MN index per 128-byte row,
-// 128-byte swizzle): 8-row groups 1024 bytes apart, 64-column blocks `lbo_bytes` apart.
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
 // Barrier among the 256 softmax threads that also ANDs a predicate.
 __device__ __forceinline__ bool softmax_all(bool ok) {
   uint32_t r;
@@ -139,9 +92,10 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
   uint64_t* kv_full = bars + 1;        // [2]
   uint64_t* kv_empty = bars + 3;       // [2]
   uint64_t* s_full = bars + 5;         // [2]  one per S buffer
-  uint64_t* p_full = bars + 7;         // [1]  256 arrivals
-  uint64_t* o_done = bars + 8;         // [1]  completes once per key tile, after its P V
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* p_full = bars + 7;         // [2]  256 arrivals; one per parity of the tile number, so
+                                       //      that the softmax threads cannot lap the MMA warp
+  uint64_t* o_done = bars + 9;         // [1]  completes once per key tile, after its P V
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int* it = items + 4 * blockIdx.z;
@@ -167,6 +121,7 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(s_full + s, 1);
     }
     mbar_init(p_full, 256);
+    mbar_init(p_full + 1, 256);
     mbar_init(o_done, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -282,7 +237,7 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_fence_after();
           issue_s(n + 1);
         }
-        if (!(ok = mbar_wait(p_full, n & 1, abort))) break;
+        if (!(ok = mbar_wait(p_full + (n & 1), (uint32_t)(n >> 1) & 1u, abort))) break;
         tc_fence_after();
         const uint32_t p_addr = smem_u32(P_OVER_K ? Ks + buf * KV_BYTES : Psep);
         const uint32_t v_addr = smem_u32(Vs + buf * KV_BYTES);
@@ -325,15 +280,16 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
       const bool need_mask = !valid || t_lo + 31 > pr || t_lo < jl;
       const int hi = valid ? pr - t_lo : -1;             // last visible column
       const int lo = jl - t_lo;                          // first visible column
-      float tmax = -INFINITY;
+      float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 32
       if (need_mask) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (j >= lo && j <= hi) tmax = fmaxf(tmax, __uint_as_float(v[j]));
+          if (j >= lo && j <= hi) t4[j & 3] = fmaxf(t4[j & 3], __uint_as_float(v[j]));
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(v[j]));
+        for (int j = 0; j < 32; ++j) t4[j & 3] = fmaxf(t4[j & 3], __uint_as_float(v[j]));
       }
+      float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
       tmax *= scale_log2;                                // the scale is positive
       float* x = xm + (n & 1) * 256;
       x[half * 128 + r] = tmax;
@@ -395,7 +351,7 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
       // P is read by the tensor core through the async proxy
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full + (n & 1));
     }
     // the row's sum from both halves, then O
     bool ok = alive && !*abort && mbar_wait(o_done, (n - 1) & 1, abort);

@@ -287,20 +287,27 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       variant: str = "auto") -> None:
     """Causal flash attention over the pages for prompt portions (bfloat16 only).
     ``items`` int32 [n, 4]: (request index, first token row, rows, first position).
-    ``variant``: ``umma`` (tcgen05 tensor cores, TMA loads; head sizes 64/128, page sizes
-    8..64 that divide 64), ``mma_sync`` (every size in DECODE_HEAD_DIMS, any page size), or
-    ``auto``: umma where it applies."""
+    ``variant``: ``umma2`` (tcgen05 tensor cores, one CTA per SM with two query tiles sharing a
+    K/V ring; head size 128, page sizes 8..64 that divide 64), ``umma`` (two CTAs of one
+    query tile per SM; head sizes 64/128, the same page sizes), ``mma_sync`` (every size in
+    DECODE_HEAD_DIMS, any page size), or ``auto``: umma2 for portions of more than 128 rows
+    where it applies, else umma where it applies, else mma_sync."""
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"prefill_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
+    if variant not in ("auto", "umma2", "umma", "mma_sync"):
+        raise KernelError(f"prefill_attention: unknown variant {variant!r}")
     _want(items, torch.int32, "items")
     page_size = k_cache.shape[2]
     umma_ok = (d in (64, 128) and 8 <= page_size <= 64 and 64 % page_size == 0
                and q.is_contiguous() and q.data_ptr() % 16 == 0)
-    if variant == "umma" and not umma_ok:
-        raise KernelError(f"prefill_attention: the umma variant does not take head_dim {d} with "
-                          f"pages of {page_size}")
-    if umma_ok and variant != "mma_sync":
-        _run("prefill_attention_umma", lib().bf_prefill_attention_umma,
+    umma2_ok = umma_ok and d == 128
+    if variant == "umma" and not umma_ok or variant == "umma2" and not umma2_ok:
+        raise KernelError(f"prefill_attention: the {variant} variant does not take head_dim {d} "
+                          f"with pages of {page_size}")
+    use2 = umma2_ok and (variant == "umma2" or (variant == "auto" and max_rows > 128))
+    if use2 or (umma_ok and variant != "mma_sync"):
+        name = "prefill_attention_umma2" if use2 else "prefill_attention_umma"
+        _run(name, getattr(lib(), "bf_" + name),
              _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
              _c_int(max_rows), _c_int(q.shape[0]), _ptr(block_tables),
              _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv), _c_int(d),

@@ -132,7 +132,7 @@ def prefill_attention(a):
     err = ops.error_word(dev)
     fn = lambda: ops.prefill_attention(q, kc, vc, items, 1, T, bt, out, nh, nkv, d, None,
                                        d ** -0.5, err,
-                                       variant=a.variant if a.variant in ("umma", "mma_sync")
+                                       variant=a.variant if a.variant in ("umma2", "umma", "mma_sync")
                                        else "auto")
     us = timed([fn], a.iters, a.warmup)
     flops = 4.0 * nh * d * (T * start + T * (T + 1) / 2)
@@ -264,7 +264,7 @@ def main(argv=None):
     ap.add_argument("--cluster", type=int, default=0,
                     help="gemm: split K over clusters of this many CTAs (needs --bn)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host, no CUDA graph")
-    ap.add_argument("--variant", default="auto", choices=["auto", "persistent", "tma", "cp_async", "umma", "mma_sync"],
+    ap.add_argument("--variant", default="auto", choices=["auto", "persistent", "tma", "cp_async", "umma2", "umma", "mma_sync"],
                     help="decode attention: tma or cp_async tile loads; prefill attention: "
                          "umma (tcgen05) or mma_sync")
     a = ap.parse_args(argv)

@@ -443,13 +443,15 @@ def test_engine_with_own_gemm_everywhere(cuda_device, tmp_path):
     (4, 2, 32, 16, None, False), (6, 1, 32, 8, None, True), (8, 2, 128, 16, None, True),
     (5, 5, 96, 4, 24, True), (3, 3, 64, 5, 70, True), (2, 1, 256, 16, 100, True),
     (4, 4, 128, 64, 130, True), (6, 2, 128, 8, None, True), (4, 1, 64, 32, 150, True)])
-@pytest.mark.parametrize("variant", ["mma_sync", "umma"])
+@pytest.mark.parametrize("variant", ["mma_sync", "umma", "umma2"])
 def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike, variant):
     """Portions that start in the middle of a prompt, straddle 64-key tiles and pages, next to
     whole prompts; the far key and the window's edge are made to stand out."""
     from binfer_b200.csrc import ops
     if variant == "umma" and not (d in (64, 128) and ps >= 8 and 64 % ps == 0):
         pytest.skip("the umma variant does not take this head or page size")
+    if variant == "umma2" and not (d == 128 and ps >= 8 and 64 % ps == 0):
+        pytest.skip("the umma2 variant does not take this head or page size")
     ctxs, qlens = [70, 200, 129, 300, 64, 2, 400], [70, 37, 5, 130, 64, 2, 290]
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
                                                    qlens, window, spike, seed=11)
@@ -469,6 +471,30 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
     ops.prefill_attention(q, kc, vc, items[1:3].contiguous(), 2, 37, bt, out2, nh, nkv, d,
                           window, d ** -0.5, err, variant=variant)
     assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("ps,window", [(64, None), (16, 300), (8, None)])
+@pytest.mark.parametrize("variant", ["umma", "umma2"])
+def test_prefill_attention_long_portions(cuda_device, ps, window, variant):
+    """Portions of many query tiles over many key tiles (the rings of stages wrap, the two
+    query tiles of a block end on different key tiles), from the start of a prompt and from
+    its middle, with and without a window."""
+    from binfer_b200.csrc import ops
+    nh, nkv, d = 4, 2, 128
+    ctxs, qlens = [1500, 700, 1100], [900, 700, 257]
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   qlens, window, True, seed=23)
+    items, row = [], 0
+    for b, (n, ql) in enumerate(zip(ctxs, qlens)):
+        items.append([b, row, ql, n - ql])
+        row += ql
+    items = torch.tensor(items, dtype=torch.int32, device=cuda_device)
+    out = torch.zeros_like(q)
+    err = _err(cuda_device)
+    ops.prefill_attention(q, kc, vc, items, len(ctxs), max(qlens), bt, out, nh, nkv, d, window,
+                          d ** -0.5, err, variant=variant)
+    assert int(err.item()) == 0
+    _close(out, ref, BF16)
 
 
 @pytest.mark.parametrize("M,N,K,bn,c", [(1, 300, 520, 64, 4), (8, 4096, 4096, 128, 4),
