@@ -11,8 +11,9 @@
 // it calls cuBLAS for every product (cuda/kernels/gemm.cu:244-267).
 //
 // Per CTA: warp 2 issues the TMA loads (token tile + BN x 64 weight tile per stage, 128-byte
-// swizzle), warp 1 issues tcgen05.mma into one TMEM accumulator, warp 0 (which may read TMEM
-// lanes 0..31; the tokens are rows 0..15) reads the accumulator.  Reduction: the tile's columns are cut
+// swizzle), warps 1 and 3 issue tcgen05.mma for the K steps in turn, each into a TMEM
+// accumulator of its own, warp 0 (which may read TMEM lanes 0..31; the tokens are rows
+// 0..15) reads and adds the accumulators.  Reduction: the tile's columns are cut
 // into C slices; CTA r owns slice r.  Every CTA writes each slice of its partial sum into
 // the owner's shared memory (st.shared::cluster), the cluster synchronises once
 // (barrier.cluster), and each owner adds the C partials of its slice in ascending rank
@@ -24,6 +25,7 @@
 // No TMA load uses multicast; every load reads this GPU's own memory.
 #include <cuda.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "tma_utils.cuh"
@@ -40,6 +42,7 @@ struct ClusterGemmParams {
   int bn;                       // feature rows per tile (multiple of 16 * cluster)
   int cluster;                  // CTAs per tile
   int stages;
+  int issuers;                  // threads that issue tcgen05.mma, 1 or 2
   long long ldo;
   int* err;
   // Fused "add into the residual stream and prepare the next norm" epilogue (resid != null):
@@ -74,7 +77,7 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, f
 }
 
 template <typename OutT>
-__global__ void __launch_bounds__(96, 1)
+__global__ void __launch_bounds__(128, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                     const ClusterGemmParams p) {
@@ -102,14 +105,14 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   const int a_bytes = CL_TOKENS * BK * 2, b_bytes = p.bn * BK * 2;
   const int stage_bytes = a_bytes + b_bytes;
   const int STAGES = p.stages;
-  constexpr int TMEM_COLS = 256;
+  constexpr int TMEM_COLS = 512;                         // two accumulators of up to 256 columns
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, min(p.issuers, max(kc1 - kc0, 1)));   // one arrival per issuing thread with work
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -157,15 +160,19 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0 && kc1 > kc0) {
+  } else if (warp == 1 || warp == 3) {
+    // Two issuing threads, K steps in turn, an accumulator each (summed by the epilogue in
+    // a fixed order): issuing a tcgen05.mma costs its thread about a hundred cycles whatever
+    // the product's size, and with one thread that, not HBM, bounded the narrow projections.
+    const int who = warp == 1 ? 0 : 1;
+    if (lane == 0 && who < p.issuers && kc1 - kc0 > who) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                              ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      int stage = 0;
-      uint32_t phase = 0;
+      const uint32_t acc = tmem_base + (uint32_t)(who * 256);
       bool ok = true;
-      for (int kc = kc0; kc < kc1; ++kc) {
-        if (!mbar_wait(full + stage, phase, abort)) {
+      for (int n = who; n < kc1 - kc0; n += p.issuers) {
+        const int stage = n % STAGES;
+        if (!mbar_wait(full + stage, (uint32_t)(n / STAGES) & 1u, abort)) {
           ok = false;
           break;
         }
@@ -175,13 +182,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         const uint64_t b_desc = umma_desc_k_sw128(a_addr + a_bytes);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
-          umma_bf16(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                    (kc > kc0 || k > 0) ? 1u : 0u);
+          umma_bf16(acc, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                    (n > who || k > 0) ? 1u : 0u);
         umma_commit(empty + stage);
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
       }
       if (ok) umma_commit(acc_full);
     }
@@ -196,6 +199,13 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       uint32_t r[16];
       if (have) {
         tmem_ld16(tmem_base + c0, r);
+        if (p.issuers == 2 && kc1 - kc0 >= 2) {          // the second issuer's share
+          uint32_t r2[16];
+          tmem_ld16(tmem_base + 256 + c0, r2);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) r[j] = 0u;     // no K steps here (or a timeout): send zeros
@@ -294,6 +304,8 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   if (stages > CL_MAX_STAGES) stages = CL_MAX_STAGES;
   if (stages < 2) return (int)cudaErrorInvalidValue;
   p.stages = stages;
+  static const int issuers = getenv("BINFER_B200_GEMM_ISSUERS") ? atoi(getenv("BINFER_B200_GEMM_ISSUERS")) : 2;
+  p.issuers = issuers == 1 ? 1 : 2;
   const size_t smem = fixed + (size_t)stages * stage_bytes;
   auto kern = gemm_cluster_kernel<OutT>;
   static bool configured = false;
@@ -306,7 +318,7 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   const int tiles = (p.features + p.bn - 1) / p.bn;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * p.cluster, 1, 1);
-  cfg.blockDim = dim3(96, 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
