@@ -43,6 +43,8 @@ struct ClusterGemmParams {
   int cluster;                  // CTAs per tile
   int stages;
   int issuers;                  // threads that issue tcgen05.mma, 1 or 2
+  int tmem_cols;                // tensor memory columns the CTA allocates (a power of two)
+  int acc_stride;               // columns between the two issuers' accumulators
   long long ldo;
   int* err;
   // Fused "add into the residual stream and prepare the next norm" epilogue (resid != null):
@@ -105,7 +107,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   const int a_bytes = CL_TOKENS * BK * 2, b_bytes = p.bn * BK * 2;
   const int stage_bytes = a_bytes + b_bytes;
   const int STAGES = p.stages;
-  constexpr int TMEM_COLS = 512;                         // two accumulators of up to 256 columns
+  const int TMEM_COLS = p.tmem_cols;                     // room for the issuers' accumulators
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -168,7 +170,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     if (lane == 0 && who < p.issuers && kc1 - kc0 > who) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                              ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      const uint32_t acc = tmem_base + (uint32_t)(who * 256);
+      const uint32_t acc = tmem_base + (uint32_t)(who * p.acc_stride);
       bool ok = true;
       for (int n = who; n < kc1 - kc0; n += p.issuers) {
         const int stage = n % STAGES;
@@ -201,7 +203,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         tmem_ld16(tmem_base + c0, r);
         if (p.issuers == 2 && kc1 - kc0 >= 2) {          // the second issuer's share
           uint32_t r2[16];
-          tmem_ld16(tmem_base + 256 + c0, r2);
+          tmem_ld16(tmem_base + (uint32_t)p.acc_stride + c0, r2);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
@@ -306,7 +308,16 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   p.stages = stages;
   static const int issuers = getenv("BINFER_B200_GEMM_ISSUERS") ? atoi(getenv("BINFER_B200_GEMM_ISSUERS")) : 2;
   p.issuers = issuers == 1 ? 1 : 2;
-  const size_t smem = fixed + (size_t)stages * stage_bytes;
+  int need = p.issuers * p.bn, cols = 32;
+  while (cols < need) cols *= 2;
+  p.tmem_cols = cols;
+  p.acc_stride = p.bn;
+  // Never less than 120 KB, so that two of these CTAs cannot share an SM: each allocates
+  // tensor memory (which blocks while another CTA holds it) and then waits for its cluster,
+  // and with two clusters' CTAs paired on the same SMs in opposite order that is a cycle.
+  // (Seen once, with the shared memory capped at 110 KB for an experiment: the launch failed.)
+  size_t smem = fixed + (size_t)stages * stage_bytes;
+  if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = gemm_cluster_kernel<OutT>;
   static bool configured = false;
   if (!configured) {

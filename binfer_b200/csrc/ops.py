@@ -7,6 +7,7 @@ loaded, or a tensor is not on a CUDA device, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
