@@ -1,4 +1,4 @@
-// bf16 matrix product for few tokens (at most 16) against a weight too narrow to give every
+// bf16 matrix product for few tokens (at most 64) against a weight too narrow to give every
 // SM a tile: out[t, f] = sum_k x[t, k] * w[f, k], with the K range split over a thread-block
 // cluster and the partial sums combined through distributed shared memory.
 //
@@ -34,7 +34,7 @@
 namespace {
 
 constexpr int CL_MAX_STAGES = 16;
-constexpr int CL_TOKENS = 16;                 // token rows fetched and reduced
+constexpr int CL_MAX_TOKENS = 64;             // token rows: 16, 32 or 64 are fetched and reduced
 constexpr int CL_BAR_BYTES = 512;
 
 struct ClusterGemmParams {
@@ -43,6 +43,7 @@ struct ClusterGemmParams {
   int cluster;                  // CTAs per tile
   int stages;
   int issuers;                  // threads that issue tcgen05.mma, 1 or 2
+  int tok_rows;                 // token rows fetched and reduced: 16, 32 or 64 (>= tokens)
   int tmem_cols;                // tensor memory columns the CTA allocates (a power of two)
   int acc_stride;               // columns between the two issuers' accumulators
   long long ldo;
@@ -79,7 +80,7 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, f
 }
 
 template <typename OutT>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(192, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                     const ClusterGemmParams p) {
@@ -95,7 +96,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // recv[rank][token][slice column]: partial sums sent to this CTA, as the owner of a slice
   float* recv = reinterpret_cast<float*>(base + CL_BAR_BYTES);
   const int slice = p.bn / p.cluster;                          // columns owned per CTA
-  const int recv_bytes = p.cluster * CL_TOKENS * slice * 4;
+  const int recv_bytes = p.cluster * p.tok_rows * slice * 4;
   uint8_t* tiles = base + CL_BAR_BYTES + ((recv_bytes + 1023) & ~1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,7 +105,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   const int kc_total = (p.K + BK - 1) / BK;
   const int kc0 = (int)((long long)kc_total * rank / p.cluster);
   const int kc1 = (int)((long long)kc_total * (rank + 1) / p.cluster);
-  const int a_bytes = CL_TOKENS * BK * 2, b_bytes = p.bn * BK * 2;
+  const int a_bytes = p.tok_rows * BK * 2, b_bytes = p.bn * BK * 2;
   const int stage_bytes = a_bytes + b_bytes;
   const int STAGES = p.stages;
   const int TMEM_COLS = p.tmem_cols;                     // room for the issuers' accumulators
@@ -162,7 +163,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       }
     }
-  } else if (warp == 1 || warp == 3) {
+  } else if (warp == 1 || warp == 3) {   // (warp 4 idles; warp 5 reads token rows 32..63)
     // Two issuing threads, K steps in turn, an accumulator each (summed by the epilogue in
     // a fixed order): issuing a tcgen05.mma costs its thread about a hundred cycles whatever
     // the product's size, and with one thread that, not HBM, bounded the narrow projections.
@@ -190,8 +191,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       }
       if (ok) umma_commit(acc_full);
     }
-  } else {
-    // warp 0: TMEM lanes 0..31; lane l holds token l of the partial sum
+  } else if (warp == 0 || (warp == 5 && p.tok_rows > 32)) {
+    // warp 0: TMEM lanes 0..31, warp 5 (more than 32 token rows): lanes 32..63; a lane holds
+    // one token's row of the partial sum
+    const int row = (warp == 0 ? 0 : 32) + lane;
+    const uint32_t lanes = (uint32_t)(warp == 0 ? 0 : 32) << 16;
     bool have = kc1 > kc0;
     if (have) have = mbar_wait(acc_full, 0, abort);
     have = __all_sync(0xffffffffu, have);
@@ -200,10 +204,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     for (int c0 = 0; c0 < p.bn; c0 += 16) {
       uint32_t r[16];
       if (have) {
-        tmem_ld16(tmem_base + c0, r);
+        tmem_ld16(tmem_base + lanes + c0, r);
         if (p.issuers == 2 && kc1 - kc0 >= 2) {          // the second issuer's share
           uint32_t r2[16];
-          tmem_ld16(tmem_base + (uint32_t)p.acc_stride + c0, r2);
+          tmem_ld16(tmem_base + lanes + (uint32_t)p.acc_stride + c0, r2);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
@@ -212,10 +216,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
         for (int j = 0; j < 16; ++j) r[j] = 0u;     // no K steps here (or a timeout): send zeros
       }
-      if (lane < CL_TOKENS) {
+      if (row < p.tok_rows) {
         const int owner = c0 / slice, col = c0 - owner * slice;
         const uint32_t dst = map_to_rank(
-            my_recv + (uint32_t)(((rank * CL_TOKENS + lane) * slice + col) * 4), (uint32_t)owner);
+            my_recv + (uint32_t)(((rank * p.tok_rows + row) * slice + col) * 4), (uint32_t)owner);
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           st_cluster_v4(dst + 16 * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
@@ -248,7 +252,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   for (int idx = threadIdx.x; idx < p.tokens * slice; idx += blockDim.x, ++j) {
     const int t = idx / slice, col = idx - t * slice;
     float sum = 0.f;
-    for (int r = 0; r < p.cluster; ++r) sum += recv[(r * CL_TOKENS + t) * slice + col];
+    for (int r = 0; r < p.cluster; ++r) sum += recv[(r * p.tok_rows + t) * slice + col];
     const int f = tile * p.bn + rank * slice + col;
     if (!p.resid) {
       if (f < p.features) bf_st(out + (size_t)t * p.ldo + f, sum);
@@ -293,13 +297,14 @@ template <typename OutT>
 int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p, long long ldx,
                    long long ldw, cudaStream_t stream) {
   CUtensorMap mx, mw;
-  int e = bf_make_tensor_map_bf16_2d(&mx, x, p.tokens, p.K, ldx, CL_TOKENS, BK);
+  p.tok_rows = p.tokens <= 16 ? 16 : p.tokens <= 32 ? 32 : 64;
+  int e = bf_make_tensor_map_bf16_2d(&mx, x, p.tokens, p.K, ldx, p.tok_rows, BK);
   if (e) return e;
   e = bf_make_tensor_map_bf16_2d(&mw, w, p.features, p.K, ldw, p.bn, BK);
   if (e) return e;
   const size_t smem_max = 226 * 1024;
-  const size_t stage_bytes = (size_t)(CL_TOKENS + p.bn) * BK * 2;
-  const size_t recv_bytes = ((size_t)CL_TOKENS * p.bn * 4 + 1023) & ~(size_t)1023;
+  const size_t stage_bytes = (size_t)(p.tok_rows + p.bn) * BK * 2;
+  const size_t recv_bytes = ((size_t)p.tok_rows * p.bn * 4 + 1023) & ~(size_t)1023;
   // behind the last stage the MMA still reads 128 token rows' worth of shared memory
   const size_t fixed = 1024 + CL_BAR_BYTES + recv_bytes + 16 * 1024;
   int stages = (int)((smem_max - fixed) / stage_bytes);
@@ -329,7 +334,7 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   const int tiles = (p.features + p.bn - 1) / p.bn;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * p.cluster, 1, 1);
-  cfg.blockDim = dim3(128, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -381,7 +386,7 @@ BF_EXPORT int bf_gemm_cluster_plan(int features, int K, int num_sms, int* bn_out
   return best_ctas;
 }
 
-// out[tokens, features] = x[tokens, K] * w[features, K]^T for tokens <= 16, the K range split
+// out[tokens, features] = x[tokens, K] * w[features, K]^T for tokens <= 64, the K range split
 // over clusters of `cluster` CTAs.  bn: feature rows per tile, a multiple of 16 * cluster,
 // at most 256.  Returns cudaErrorInvalidValue for what it does not take.
 BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int tokens,
@@ -389,7 +394,7 @@ BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int 
                                    long long ldo, int out_dtype, int bn, int cluster, int* err,
                                    cudaStream_t stream) {
   if (tokens <= 0 || features <= 0) return 0;
-  if (tokens > CL_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
+  if (tokens > CL_MAX_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
       ((uintptr_t)w & 15))
     return (int)cudaErrorInvalidValue;
   if ((cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
@@ -427,7 +432,7 @@ BF_EXPORT int bf_gemm_bf16_cluster_add_norm(const void* x, const void* w, int to
                                             float* partials, int* n_partials, int* err,
                                             cudaStream_t stream) {
   if (tokens <= 0 || features <= 0) return 0;
-  if (tokens > CL_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
+  if (tokens > CL_MAX_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
       ((uintptr_t)w & 15) || !resid || !norm_w || !xt || !partials)
     return (int)cudaErrorInvalidValue;
   if ((cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||

@@ -387,14 +387,17 @@ def gemm_cluster_plan(features: int, K: int, device: torch.device):
     return (bn.value, c.value) if n > 0 else None
 
 
+CLUSTER_MAX_TOKENS = 64
+
+
 def gemm_bf16_cluster(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
                       bn: int, cluster: int) -> bool:
-    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 16 with the K range split over clusters of
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64 with the K range split over clusters of
     ``cluster`` CTAs (partials combined through distributed shared memory).  Returns False,
     having done nothing, for shapes the kernel does not take."""
     M, K = x.shape
     N = w.shape[0]
-    if (M > 16 or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
+    if (M > CLUSTER_MAX_TOKENS or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
             or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or out.stride(1) != 1):
         return False
     _run("gemm_bf16_cluster", lib().bf_gemm_bf16_cluster, _ptr(x), _ptr(w), _ptr(out), _c_int(M),
@@ -408,11 +411,11 @@ def gemm_bf16_cluster_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Te
                                cluster: int):
     """``resid += x @ w^T`` (float32 stream ``[M, N]``), and the next norm's output short of its
     row factor: returns ``(xt, RowScale)`` with ``xt = bfloat16(resid * norm_w)``, or None,
-    having done nothing, for shapes the kernel does not take (M <= 16, see
+    having done nothing, for shapes the kernel does not take (M <= 64, see
     ``gemm_bf16_cluster``)."""
     M, K = x.shape
     N = w.shape[0]
-    if (M > 16 or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
+    if (M > CLUSTER_MAX_TOKENS or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
             or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16
             or resid.dtype != torch.float32 or resid.shape != (M, N) or resid.stride(1) != 1
             or norm_w.dtype != torch.float32 or norm_w.numel() != N or not norm_w.is_contiguous()):

@@ -285,7 +285,8 @@ def test_decode_attention_more_splits_than_one_merge_pass(cuda_device, variant):
 
 
 @pytest.mark.parametrize("M,N,K,bn,c", [(8, 4096, 4096, 128, 4), (3, 200, 512, 64, 2),
-                                        (16, 1000, 320, 80, 1)])
+                                        (16, 1000, 320, 80, 1), (64, 4096, 4096, 128, 4),
+                                        (37, 1024, 2048, 64, 4)])
 def test_gemm_cluster_adds_into_the_stream_and_prepares_the_norm(cuda_device, M, N, K, bn, c):
     """resid += x w^T in float; xt = bf16(resid * norm_w); the partial sums of squares add up
     to the rows' sums, so that xt times the factor is the RMSNorm of the new stream."""
@@ -501,7 +502,9 @@ def test_prefill_attention_long_portions(cuda_device, ps, window, variant):
                                         (16, 1000, 4104, 128, 8), (7, 6144, 4096, 192, 4),
                                         (3, 256, 256, 256, 2), (16, 4096, 12288, 128, 4),
                                         (5, 96, 64, 64, 4), (8, 24576, 4096, 176, 1),
-                                        (2, 1000, 320, 80, 1)])
+                                        (2, 1000, 320, 80, 1), (17, 4096, 4096, 128, 4),
+                                        (40, 520, 1024, 64, 2), (64, 4096, 12288, 128, 4),
+                                        (33, 6144, 4096, 192, 4)])
 @pytest.mark.parametrize("out_dtype", [BF16, F32])
 def test_gemm_bf16_cluster_split_k(cuda_device, M, N, K, bn, c, out_dtype):
     """K split over a cluster and reduced through distributed shared memory; widths and depths
@@ -523,6 +526,6 @@ def test_gemm_bf16_cluster_split_k(cuda_device, M, N, K, bn, c, out_dtype):
     again = torch.empty_like(out)
     assert ops.gemm_bf16_cluster(x, w, again, err, bn, c)
     assert torch.equal(again, out), "the split-K sum must have one fixed order"
-    assert not ops.gemm_bf16_cluster(torch.zeros(17, K, device=cuda_device, dtype=BF16), w,
-                                     torch.empty(17, N, device=cuda_device, dtype=out_dtype),
+    assert not ops.gemm_bf16_cluster(torch.zeros(65, K, device=cuda_device, dtype=BF16), w,
+                                     torch.empty(65, N, device=cuda_device, dtype=out_dtype),
                                      err, bn, c)
