@@ -38,6 +38,16 @@ TINY_M = dict(
     use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
     attention_bias=False)
 
+# the same sizes with a window on two of three layers: the TMA / tcgen05 attention kernels
+# with keys that fall out of the window, and pages that are given back while a request runs
+TINY_V = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=3, hidden_size=256,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=384,
+    vocab_size=410, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
+    use_sliding_window=True, sliding_window=150,
+    layer_types=["sliding_attention", "full_attention", "sliding_attention"],
+    max_position_embeddings=4096, hidden_act="silu", attention_bias=False)
+
 # wide enough (2048 inputs to the output and down projections) for the decode step's
 # split-K cluster products, and with them the products that prepare the next norm
 TINY_F = dict(
@@ -48,6 +58,7 @@ TINY_F = dict(
     attention_bias=False)
 
 TINY = {
+    "V": dict(raw=TINY_V, std=0.05, norm_std=0.02, page_size=32, seed=66),
     "F": dict(raw=TINY_F, std=0.03, norm_std=0.05, page_size=64, seed=55),
     "M": dict(raw=TINY_M, std=0.05, norm_std=0.02, page_size=16, seed=44),
     "A": dict(raw=TINY_A, std=0.02, norm_std=0.01, page_size=16, seed=11),

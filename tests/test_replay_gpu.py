@@ -18,7 +18,7 @@ TOL = {torch.float32: 2e-5, torch.bfloat16: 3e-2}
 TOL_RMS = {torch.float32: 5e-6, torch.bfloat16: 1e-2}
 
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 70], "W": [3, 30, 64, 101],
-           "M": [2, 45, 150, 333], "F": [3, 40, 70, 130]}
+           "M": [2, 45, 150, 333], "F": [3, 40, 70, 130], "V": [4, 160, 333, 500]}
 
 
 def _requests(which, extra=()):
@@ -70,7 +70,7 @@ def _compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["A", "B", "W", "M"])
+@pytest.mark.parametrize("which", ["A", "B", "W", "M", "V"])
 @pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
 def test_replay(cuda_device, plain_logits, which, dtype, regime):
     extra = (55, 61) if regime == "mixed" else ()
@@ -87,7 +87,7 @@ def test_replay(cuda_device, plain_logits, which, dtype, regime):
     _compare(got, ref, dtype, f"{which}/{regime}")
 
 
-@pytest.mark.parametrize("which", ["A", "B", "W", "M"])
+@pytest.mark.parametrize("which", ["A", "B", "W", "M", "V"])
 def test_regimes_agree_bitwise_in_float32(cuda_device, plain_logits, which):
     """In float32 the order of every sum is fixed by the position alone, so cutting
     and batching change nothing at all."""
@@ -187,3 +187,25 @@ def test_replay_with_products_that_prepare_the_next_norm(cuda_device, plain_logi
         outs.append(got)
     worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
     assert worst <= TOL[dtype], f"fused and unfused steps differ by {worst:.3g}"
+
+
+def test_long_context_bfloat16(cuda_device, plain_logits):
+    """A prompt of 2600 tokens (portions of 2048 and the rest), then 40 tokens one by one: the
+    tcgen05 prefill kernels over many key tiles, the decode kernels over 21 splits, and the
+    graph-captured step, against the plain implementation."""
+    which, dtype = "M", torch.bfloat16
+    vocab = H.TINY[which]["raw"]["vocab_size"]
+    reqs = {"long": H.random_tokens(2640, vocab, 17)}
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    toks = reqs["long"]
+    steps = [{"step": 0, "entries": [{"id": "long", "tokens": toks[:2048], "want": [0, 2047]}], "end": []},
+             {"step": 1, "entries": [{"id": "long", "tokens": toks[2048:2600],
+                                      "want": [0, 551]}], "end": []}]
+    for i in range(2600, 2640):
+        steps.append({"step": len(steps), "entries": [{"id": "long", "tokens": [toks[i]], "want": [0]}],
+                      "end": ["long"] if i == 2639 else []})
+    runner = _runner(model_dir, dtype, 64, H.peak_pages(steps, 64))
+    runner.enable_decode_graphs(max_batch=2, max_seq_len=4096)
+    got = H.run_trace(runner, steps)
+    worst = max(H.rel_err(row, ref["long"][pos]) for (rid, pos), row in got.items())
+    assert len(got) == 44 and worst <= TOL[dtype], worst
