@@ -14,6 +14,8 @@ from .base import (BuildEnv, EntryView, Part, ResidualStream, ScaledRows, StepCo
 
 
 class PreNormBlock(Part):
+    takes_successor = True      # forward(stream, ctx, view, successor): see DecoderModel.forward
+
     def __init__(self, spec: LayerSpec, hidden_size: int, names: NameLayout, index: int,
                  env: BuildEnv):
         p = names.layer_prefix.format(i=index)

@@ -121,8 +121,13 @@ class DecoderModel:
         last = len(spec.schedule) - 1
         for e, entry in enumerate(spec.schedule):
             ctx.entry = e
-            nxt = self.blocks[spec.schedule[e + 1].layer] if e < last else None
-            self.blocks[entry.layer].forward(stream, ctx, views[e], nxt)
+            block = self.blocks[entry.layer]
+            if getattr(block, "takes_successor", False):
+                # a block may let its last product prepare the next block's first norm
+                nxt = self.blocks[spec.schedule[e + 1].layer] if e < last else None
+                block.forward(stream, ctx, views[e], nxt)
+            else:
+                block.forward(stream, ctx, views[e])
         R = ctx.logit_rows.shape[0]
         if R == 0:
             stream.flush()
