@@ -52,6 +52,7 @@ constexpr int A2_THREADS = 608;  // sixteen softmax warps, the TMA warp, two MMA
 constexpr int A2_TMA_WARP = 16;
 constexpr int A2_MMA_WARP = 17;  // 17 issues for query tile A, 18 for tile B
 constexpr int A2_D = 128;
+constexpr int A2_STAGGER_CYCLES = 1200;
 
 // Barrier among the 256 softmax threads of a group that also ANDs a predicate.
 __device__ __forceinline__ bool group_all(int id, bool ok) {
@@ -74,7 +75,7 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                                const int* __restrict__ items,
                                const int* __restrict__ block_tables, int table_stride,
                                __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size,
-                               int num_pages, int window, float scale_log2,
+                               int num_pages, int window, float scale_log2, int stagger,
                                int* __restrict__ err) {
   constexpr int D = A2_D;
   constexpr int HALVES = D / 64;
@@ -245,6 +246,15 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         if (grp == 1) umma_commit(k_dead + n % A2_STAGES);   // tile A may then write P over K
       };
       bool ok = mbar_wait(q_full, 0, abort) && mbar_wait(kv_full, 0, abort);
+      // tile B starts about half a tile's softmax after tile A: the two groups then stay out
+      // of step, one's exponentials under the other's loads, maxima and stores, instead of
+      // queueing for the same unit at the same time.  (It cannot wait for A's first P instead:
+      // A writes that over the K tile, which needs B's first product done.)
+      if (ok && grp == 1 && tiles >= 8) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < stagger) {
+        }
+      }
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -476,6 +486,7 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
   dim3 grid((max_rows + 2 * A2_BM - 1) / (2 * A2_BM), nh, n_items);
   kern<<<grid, A2_THREADS, smem, stream>>>(mq, mk, mv, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
-                                           window, scale * 1.4426950408889634f, err);
+                                           window, scale * 1.4426950408889634f,
+                                           A2_STAGGER_CYCLES, err);
   return bf_launch_status();
 }
