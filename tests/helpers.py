@@ -48,6 +48,16 @@ TINY_V = dict(
     layer_types=["sliding_attention", "full_attention", "sliding_attention"],
     max_position_embeddings=4096, hidden_act="silu", attention_bias=False)
 
+# sizes that are no power of two at the scale where the decode step's cluster products, the
+# persistent decode attention (6 query heads per kv head) and the tcgen05 head product run:
+# a width of 1536, 4480 inner features, a vocabulary of 5001
+TINY_O = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=1536,
+    num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=4480,
+    vocab_size=5001, rope_theta=5e5, rms_norm_eps=2e-6, tie_word_embeddings=False,
+    use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
+    attention_bias=False)
+
 # wide enough (2048 inputs to the output and down projections) for the decode step's
 # split-K cluster products, and with them the products that prepare the next norm
 TINY_F = dict(
@@ -58,6 +68,7 @@ TINY_F = dict(
     attention_bias=False)
 
 TINY = {
+    "O": dict(raw=TINY_O, std=0.03, norm_std=0.05, page_size=64, seed=77),
     "V": dict(raw=TINY_V, std=0.05, norm_std=0.02, page_size=32, seed=66),
     "F": dict(raw=TINY_F, std=0.03, norm_std=0.05, page_size=64, seed=55),
     "M": dict(raw=TINY_M, std=0.05, norm_std=0.02, page_size=16, seed=44),
