@@ -45,7 +45,7 @@ class AttentionSpec:
     bias: bool = False           # q/k/v/o projection biases
     window: Optional[int] = None  # keys j with p - window < j <= p; None = all keys
     scale: Optional[float] = None  # None = 1/sqrt(head_dim)
-    position: Optional[RopeSpec] = None
+    position: Optional[object] = None   # RopeSpec, or any spec whose kind is registered
 
     @property
     def group_size(self) -> int:

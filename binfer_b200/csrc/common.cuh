@@ -166,7 +166,9 @@ __device__ __forceinline__ void bf_trace_point(int code) {
 #define BF_TRACE_POINT(code)
 #define BF_TRACE_READER(name)
 #endif
-// kernel ids of the trace codes (code = 10 * id + phase; phase 0 start, 1 after the wait, 2 end)
+// kernel ids of the trace codes (code = 10 * id + phase; phase 0 start, 1 after the wait, 2 end;
+// the cluster product also 5: its products are done, 3: its sums are sent, 4: the cluster's
+// barrier is passed)
 #define BF_TR_RMSNORM 1
 #define BF_TR_SILU 2
 #define BF_TR_QKNORM 3

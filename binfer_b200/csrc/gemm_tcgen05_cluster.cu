@@ -12,13 +12,14 @@
 //
 // Per CTA: warp 2 issues the TMA loads (token tile + BN x 64 weight tile per stage, 128-byte
 // swizzle), warps 1 and 3 issue tcgen05.mma for the K steps in turn, each into a TMEM
-// accumulator of its own, warp 0 (which may read TMEM lanes 0..31; the tokens are rows
-// 0..15) reads and adds the accumulators.  Reduction: the tile's columns are cut
-// into C slices; CTA r owns slice r.  Every CTA writes each slice of its partial sum into
-// the owner's shared memory (st.shared::cluster), the cluster synchronises once
-// (barrier.cluster), and each owner adds the C partials of its slice in ascending rank
-// order and stores the result: one fixed order of summation, no atomics, no global
-// workspace, and nothing spins on another CTA (the cluster barrier is the hardware's).
+// accumulator of its own, warps 0 and 4 (which may read TMEM lanes 0..31; the tokens are rows
+// 0..15) read and add the accumulators, half of the tile's columns each.  Reduction: the
+// tile's columns are cut into C slices; CTA r owns slice r.  Every CTA writes each slice of
+// its partial sum into the owner's shared memory (st.shared::cluster, laid out so that the
+// lanes of a store are neighbours there), the cluster synchronises once (barrier.cluster),
+// and each owner adds the C partials of its slice in ascending rank order and stores the
+// result: one fixed order of summation, no atomics, no global workspace, and nothing spins
+// on another CTA (the cluster barrier is the hardware's).
 //
 // mbarrier waits are bounded (about a second); on a timeout the CTA sets BF_ERR_WAIT,
 // still contributes (zeros) and still joins the cluster barrier, frees TMEM and returns.
@@ -56,6 +57,22 @@ struct ClusterGemmParams {
   __nv_bfloat16* xt;
   float* partials;
   long long ldr, ldxt;
+  // Fused "head norms, rotation and store into the pages" epilogue of the q/k/v projection
+  // (q_out != null): a tile's columns are whole heads (bn a multiple of d) and the tile's
+  // rows are shared out by token, token t to CTA t % cluster, so that an owner holds whole
+  // heads of its tokens.  `out` is not written then.
+  const float* q_w;             // per-head norm weights, null: no norm
+  const float* k_w;
+  const float* inv_freq;        // rot_half rotation frequencies, null: no rotation
+  const int* positions;
+  const int* slots;             // place of each token in the pages; negative: store nothing
+  __nv_bfloat16* q_out;         // [tokens, nh * d]
+  __nv_bfloat16* k_cache;       // [pages, nkv, page_size, d]; null with nkv = 0
+  __nv_bfloat16* v_cache;
+  int nh, nkv, d, rot_half, page_size;
+  long long num_slots;
+  float head_eps;
+  BfRowScale rs;                // factor on the rows of the product (the norm before it)
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -79,6 +96,38 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, f
                : "memory");
 }
 
+// ---- the q/k/v form's epilogue: what a warp needs of a token, and the rotation
+struct QkvToken {
+  int slot;
+  float factor;                 // of the norm before the projection
+  float sn[4], cs[4];           // of the lane's rotation pairs (frequencies lane + 32 j)
+};
+__device__ __forceinline__ QkvToken qkv_token(const ClusterGemmParams& p, int t, int lane) {
+  QkvToken k;
+  const BfRowShare share = bf_row_fetch(p.rs, t, lane);
+  k.slot = p.k_cache ? p.slots[t] : -1;
+  const float pos = p.inv_freq ? (float)p.positions[t] : 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    k.sn[j] = 0.f;
+    k.cs[j] = 1.f;
+    if (lane + 32 * j < p.rot_half) sincosf(pos * p.inv_freq[lane + 32 * j], &k.sn[j], &k.cs[j]);
+  }
+  k.factor = bf_row_finish(p.rs, share);
+  return k;
+}
+// a lane holds the head's elements lane + 32 j; element i < rot_half turns with element
+// i + rot_half, which is M = rot_half / 32 places further in the same lane
+template <int M>
+__device__ __forceinline__ void rotate_pairs(float (&v)[8], const QkvToken& k) {
+#pragma unroll
+  for (int j = 0; j < M; ++j) {
+    const float a = v[j], b = v[j + M];
+    v[j] = a * k.cs[j] - b * k.sn[j];
+    v[j + M] = a * k.sn[j] + b * k.cs[j];
+  }
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -96,7 +145,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // recv[rank][token][slice column]: partial sums sent to this CTA, as the owner of a slice
   float* recv = reinterpret_cast<float*>(base + CL_BAR_BYTES);
   const int slice = p.bn / p.cluster;                          // columns owned per CTA
-  const int recv_bytes = p.cluster * p.tok_rows * slice * 4;
+  const int own_tokens = (p.tokens + p.cluster - 1) / p.cluster;   // (q/k/v form) per CTA
+  const int recv_bytes = p.q_out ? p.cluster * own_tokens * p.bn * 4
+                                 : p.cluster * p.tok_rows * slice * 4;
   uint8_t* tiles = base + CL_BAR_BYTES + ((recv_bytes + 1023) & ~1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,7 +214,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       }
     }
-  } else if (warp == 1 || warp == 3) {   // (warp 4 idles; warp 5 reads token rows 32..63)
+  } else if (warp == 1 || warp == 3) {
     // Two issuing threads, K steps in turn, an accumulator each (summed by the epilogue in
     // a fixed order): issuing a tcgen05.mma costs its thread about a hundred cycles whatever
     // the product's size, and with one thread that, not HBM, bounded the narrow projections.
@@ -191,83 +242,188 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       }
       if (ok) umma_commit(acc_full);
     }
-  } else if (warp == 0 || (warp == 5 && p.tok_rows > 32)) {
-    // warp 0: TMEM lanes 0..31, warp 5 (more than 32 token rows): lanes 32..63; a lane holds
-    // one token's row of the partial sum
-    const int row = (warp == 0 ? 0 : 32) + lane;
-    const uint32_t lanes = (uint32_t)(warp == 0 ? 0 : 32) << 16;
+  } else if (warp == 0 || warp == 4 || (warp == 5 && p.tok_rows > 32)) {
+    // Warps 0 and 4 may both read TMEM lanes 0..31 and share the tile's columns; warp 5 (more
+    // than 32 token rows) reads lanes 32..63.  A lane holds one token's row of the partial sum.
+    const int row = (warp == 5 ? 32 : 0) + lane;
+    const uint32_t lanes = (uint32_t)(warp == 5 ? 32 : 0) << 16;
+    const int chunks = p.bn / 16, half = (chunks + 1) / 2;
+    const int c_begin = warp == 4 ? half * 16 : 0, c_end = warp == 0 ? half * 16 : p.bn;
     bool have = kc1 > kc0;
     if (have) have = mbar_wait(acc_full, 0, abort);
     have = __all_sync(0xffffffffu, have);
     tc_fence_after();
+    BF_TRACE_POINT(10 * BF_TR_GEMM + 5);
     const uint32_t my_recv = smem_u32(recv);
-    for (int c0 = 0; c0 < p.bn; c0 += 16) {
+    for (int c0 = c_begin; c0 < c_end; c0 += 16) {
       uint32_t r[16];
       if (have) {
-        tmem_ld16(tmem_base + lanes + c0, r);
-        if (p.issuers == 2 && kc1 - kc0 >= 2) {          // the second issuer's share
+        if (p.issuers == 2 && kc1 - kc0 >= 2) {          // with the second issuer's share
           uint32_t r2[16];
-          tmem_ld16(tmem_base + lanes + (uint32_t)p.acc_stride + c0, r2);
+          tmem_ld16_pair(tmem_base + lanes + c0, tmem_base + lanes + (uint32_t)p.acc_stride + c0,
+                         r, r2);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        } else {
+          tmem_ld16(tmem_base + lanes + c0, r);
         }
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) r[j] = 0u;     // no K steps here (or a timeout): send zeros
       }
-      if (row < p.tok_rows) {
-        const int owner = c0 / slice, col = c0 - owner * slice;
-        const uint32_t dst = map_to_rank(
-            my_recv + (uint32_t)(((rank * p.tok_rows + row) * slice + col) * 4), (uint32_t)owner);
+      if (p.q_out) {
+        // the token's owner gets its whole row: recv[rank][own token][column]
+        if (row < p.tokens) {
+          const int at = (rank * own_tokens + row / p.cluster) * p.bn + c0;
+          const uint32_t dst =
+              map_to_rank(my_recv + (uint32_t)(at * 4), (uint32_t)(row % p.cluster));
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            st_cluster_v4(dst + 16 * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        }
+      } else if (row < p.tokens) {                        // (rows beyond are padding: never read)
+        // the owner of these 16 columns gets them as recv[rank][group of 4 columns][token][4]:
+        // the lanes of one store are then neighbours in the owner's shared memory (with the
+        // token's row contiguous instead, every lane's 16 bytes went to a line of their own,
+        // and the send took 2.5 to 3.9 us of a product's 10 to 15)
+        const int owner = c0 / slice, group = (c0 - owner * slice) / 4;
+        const int at = ((rank * (slice / 4) + group) * p.tok_rows + row) * 4;
+        const uint32_t dst = map_to_rank(my_recv + (uint32_t)(at * 4), (uint32_t)owner);
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          st_cluster_v4(dst + 16 * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          st_cluster_v4(dst + (uint32_t)(q * p.tok_rows * 16), __uint_as_float(r[4 * q]),
+                        __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                        __uint_as_float(r[4 * q + 3]));
       }
     }
     tc_fence_before();
   }
 
-  // the fused epilogue's inputs do not depend on the product: they are asked for before the
-  // cluster waits for its slowest member (up to four elements a thread; more are read later)
-  float pre_r[4], pre_w[4];
-  if (p.resid) {
+  // The plain forms' work after the barrier: an item is 4 neighbouring columns of one token.
+  // The fused epilogue's inputs do not depend on the product: those of a thread's first item
+  // are asked for before the cluster waits for its slowest member (further items' later).
+  const int groups = slice / 4;
+  const int n_plain = p.q_out ? 0 : p.tokens * groups;
+  float pre_r[4] = {0.f, 0.f, 0.f, 0.f}, pre_w[4] = {0.f, 0.f, 0.f, 0.f};
+  if (p.resid && (int)threadIdx.x < n_plain) {
+    const int g = threadIdx.x / p.tokens, t = threadIdx.x - g * p.tokens;
+    const int f = tile * p.bn + rank * slice + g * 4;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int idx = threadIdx.x + j * blockDim.x;
-      const int t = idx / slice, col = idx - t * slice;
-      const int f = tile * p.bn + rank * slice + col;
-      const bool in = idx < p.tokens * slice && f < p.features;
-      pre_r[j] = in ? p.resid[(size_t)t * p.ldr + f] : 0.f;
-      pre_w[j] = in ? p.norm_w[f] : 0.f;
-    }
+    for (int k = 0; k < 4; ++k)
+      if (f + k < p.features) {
+        pre_r[k] = p.resid[(size_t)t * p.ldr + f + k];
+        pre_w[k] = p.norm_w[f + k];
+      }
   }
 
+  // the q/k/v form: a warp per token of this CTA, which walks the tile's heads; what the
+  // warp's first token needs beside the product (its place, the row's factor, the sines) is
+  // asked for before the cluster's barrier.  The warps take their turns in the order in which
+  // they are free: 2 has issued its loads long before the sums are there, 5 idles unless there
+  // are more than 32 token rows, 1 and 3 issue products to the end, 4 and 0 send.
+  const int heads_per_tile = p.q_out ? p.bn / p.d : 0;
+  const int n_mine = p.q_out && p.tokens > rank ? (p.tokens - rank + p.cluster - 1) / p.cluster : 0;
+  const int turn = warp == 2 ? 0 : warp == 5 ? 1 : warp == 1 ? 2 : warp == 3 ? 3 : warp == 4 ? 4 : 5;
+  QkvToken tk;
+  if (turn < n_mine) tk = qkv_token(p, turn * p.cluster + rank, lane);
+
   // every thread of every CTA of the cluster: partials are in place after this
+  BF_TRACE_POINT(10 * BF_TR_GEMM + 3);
   cluster_sync_all();
+  BF_TRACE_POINT(10 * BF_TR_GEMM + 4);
+
+  for (int it = turn * heads_per_tile; it < n_mine * heads_per_tile; ++it) {
+    const int lt = it / heads_per_tile, hh = it - lt * heads_per_tile;
+    if (hh == heads_per_tile - 1) it += 5 * heads_per_tile;      // on to the token 6 further
+    const int t = lt * p.cluster + rank;
+    if (lt != turn && hh == 0) tk = qkv_token(p, t, lane);
+    const int head = tile * p.bn / p.d + hh;
+    if (head >= p.nh + 2 * p.nkv) continue;
+    const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+    if (!is_q && tk.slot < 0) continue;
+    const int nj = p.d >> 5;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float sum = 0.f;
+      if (j < nj)
+        for (int r = 0; r < p.cluster; ++r)                // ascending rank: one fixed order
+          sum += recv[(r * own_tokens + lt) * p.bn + hh * p.d + lane + 32 * j];
+      v[j] = sum * tk.factor;
+    }
+    if (is_q || is_k) {
+      const float* w = is_q ? p.q_w : p.k_w;
+      if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+        const float inv = rsqrtf(warp_sum(ss) / (float)p.d + p.head_eps);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nj) v[j] *= inv * w[lane + 32 * j];
+      }
+      switch (p.rot_half >> 5) {
+        case 1: rotate_pairs<1>(v, tk); break;
+        case 2: rotate_pairs<2>(v, tk); break;
+        case 3: rotate_pairs<3>(v, tk); break;
+        case 4: rotate_pairs<4>(v, tk); break;
+        default: break;
+      }
+    }
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = p.q_out + ((size_t)t * p.nh + head) * p.d;
+    } else {
+      if ((long long)tk.slot >= p.num_slots) {
+        if (lane == 0) atomicOr(p.err, BF_ERR_SLOT);
+        continue;
+      }
+      const int h = is_k ? head - p.nh : head - p.nh - p.nkv;
+      const int page = tk.slot / p.page_size, off = tk.slot - page * p.page_size;
+      dst = (is_k ? p.k_cache : p.v_cache) + (((size_t)page * p.nkv + h) * p.page_size + off) * p.d;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < nj) dst[lane + 32 * j] = __float2bfloat16_rn(v[j]);
+  }
 
   // this CTA's slice: add the partials in ascending rank order, store
-  int j = 0;
-  for (int idx = threadIdx.x; idx < p.tokens * slice; idx += blockDim.x, ++j) {
-    const int t = idx / slice, col = idx - t * slice;
-    float sum = 0.f;
-    for (int r = 0; r < p.cluster; ++r) sum += recv[(r * p.tok_rows + t) * slice + col];
-    const int f = tile * p.bn + rank * slice + col;
+  for (int idx = threadIdx.x; idx < n_plain; idx += blockDim.x) {
+    const int g = idx / p.tokens, t = idx - g * p.tokens;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < p.cluster; ++r) {
+      const float4 v =
+          *reinterpret_cast<const float4*>(recv + ((r * groups + g) * p.tok_rows + t) * 4);
+      sum[0] += v.x;
+      sum[1] += v.y;
+      sum[2] += v.z;
+      sum[3] += v.w;
+    }
+    const int f = tile * p.bn + rank * slice + g * 4;
     if (!p.resid) {
-      if (f < p.features) bf_st(out + (size_t)t * p.ldo + f, sum);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (f + k < p.features) bf_st(out + (size_t)t * p.ldo + f + k, sum[k]);
     } else {
-      float x = 0.f;
-      if (f < p.features) {
-        float* rp = p.resid + (size_t)t * p.ldr + f;
-        // (the selects keep pre_r and pre_w in registers)
-        const float r0 = j == 0 ? pre_r[0] : j == 1 ? pre_r[1] : j == 2 ? pre_r[2] : pre_r[3];
-        const float w0 = j == 0 ? pre_w[0] : j == 1 ? pre_w[1] : j == 2 ? pre_w[2] : pre_w[3];
-        x = (j < 4 ? r0 : *rp) + sum;
-        *rp = x;
-        p.xt[(size_t)t * p.ldxt + f] = __float2bfloat16_rn(x * (j < 4 ? w0 : p.norm_w[f]));
+      const bool first = idx == (int)threadIdx.x;
+      float sq[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float x = 0.f;
+        if (f + k < p.features) {
+          float* rp = p.resid + (size_t)t * p.ldr + f + k;
+          x = (first ? pre_r[k] : *rp) + sum[k];
+          *rp = x;
+          p.xt[(size_t)t * p.ldxt + f + k] =
+              __float2bfloat16_rn(x * (first ? pre_w[k] : p.norm_w[f + k]));
+        }
+        sq[k] = x * x;
       }
-      recv[t * slice + col] = x * x;                     // rank 0's part of recv: read above, by this thread
+      // rank 0's part of recv, which this thread has read: now the squares
+      *reinterpret_cast<float4*>(recv + (g * p.tok_rows + t) * 4) =
+          make_float4(sq[0], sq[1], sq[2], sq[3]);
     }
   }
   if (p.resid) {
@@ -275,7 +431,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     __syncthreads();
     for (int t = threadIdx.x; t < p.tokens; t += blockDim.x) {
       float sq = 0.f;
-      for (int col = 0; col < slice; ++col) sq += recv[t * slice + col];
+      for (int col = 0; col < slice; ++col) sq += recv[((col >> 2) * p.tok_rows + t) * 4 + (col & 3)];
       p.partials[(size_t)t * gridDim.x + blockIdx.x] = sq;
     }
   }
@@ -304,7 +460,9 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   if (e) return e;
   const size_t smem_max = 226 * 1024;
   const size_t stage_bytes = (size_t)(p.tok_rows + p.bn) * BK * 2;
-  const size_t recv_bytes = ((size_t)p.tok_rows * p.bn * 4 + 1023) & ~(size_t)1023;
+  const size_t recv_rows =
+      p.q_out ? (size_t)p.cluster * ((p.tokens + p.cluster - 1) / p.cluster) : (size_t)p.tok_rows;
+  const size_t recv_bytes = (recv_rows * p.bn * 4 + 1023) & ~(size_t)1023;
   // behind the last stage the MMA still reads 128 token rows' worth of shared memory
   const size_t fixed = 1024 + CL_BAR_BYTES + recv_bytes + 16 * 1024;
   int stages = (int)((smem_max - fixed) / stage_bytes);
@@ -400,7 +558,7 @@ BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int 
   if ((cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
       bn % (16 * cluster))
     return (int)cudaErrorInvalidValue;
-  ClusterGemmParams p;
+  ClusterGemmParams p = {};
   p.tokens = tokens;
   p.features = features;
   p.K = K;
@@ -438,7 +596,7 @@ BF_EXPORT int bf_gemm_bf16_cluster_add_norm(const void* x, const void* w, int to
   if ((cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) || bn <= 0 || bn > 256 ||
       bn % (16 * cluster))
     return (int)cudaErrorInvalidValue;
-  ClusterGemmParams p;
+  ClusterGemmParams p = {};
   p.tokens = tokens;
   p.features = features;
   p.K = K;
@@ -454,6 +612,123 @@ BF_EXPORT int bf_gemm_bf16_cluster_add_norm(const void* x, const void* w, int to
   p.ldr = ldr;
   p.ldxt = ldxt;
   if (n_partials) *n_partials = ((features + bn - 1) / bn) * cluster;
+  return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
+}
+
+// How many clusters of c CTAs of this kernel can be resident at once (0 on an error).
+static int resident_clusters(int c) {
+  static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (c < 1 || c > 8) return 0;
+  if (known[c] >= 0) return known[c];
+  auto kern = gemm_cluster_kernel<__nv_bfloat16>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(c * 148, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = 200 * 1024;              // one CTA an SM, as every launch of it has
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = c;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int resident = 0;
+  if (cudaOccupancyMaxActiveClusters(&resident, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return known[c] = resident;
+}
+
+// Tile and cluster for the q/k/v form: tiles of whole heads (bn a multiple of d, at most 256),
+// clusters of 1 to 8 CTAs that each keep at least 4 K-steps, all clusters resident at once
+// (asked of the occupancy calculator: clusters do not straddle GPCs, so the SM count alone
+// does not tell).  The narrowest tile that gives at least min_ctas CTAs, with the largest
+// such cluster: the time after the last weight byte grows with the tile's width (one warp
+// sends the sums), and measured on the 8B shape 96 CTAs of 128 rows (13.3 us) beat 128 of 192
+// (13.7) and 120 of 256 (15.0 and more).  If no arrangement gives min_ctas: the one with the
+// most CTAs.  Returns the number of CTAs or 0.  Needs a device.
+BF_EXPORT int bf_gemm_cluster_qkv_plan(int features, int K, int d, int num_sms, int min_ctas,
+                                       int* bn_out, int* cluster_out) {
+  if (d <= 0 || d % 32 || d > 256) return 0;
+  const int kc = (K + BK - 1) / BK;
+  int best_ctas = 0, best_bn = 0, best_c = 0;
+  for (int bn = d; bn <= 256; bn += d) {
+    const int tiles = (features + bn - 1) / bn;
+    for (int c = 8; c >= 1; --c) {
+      const int ctas = tiles * c;
+      if (kc / c < 4 || ctas > num_sms || ctas <= best_ctas) continue;
+      if (resident_clusters(c) < tiles) continue;
+      best_ctas = ctas;
+      best_bn = bn;
+      best_c = c;
+      break;                                      // smaller clusters of this tile: fewer CTAs
+    }
+    if (best_ctas >= min_ctas && min_ctas > 0) break;
+  }
+  if (best_ctas == 0) return 0;
+  *bn_out = best_bn;
+  *cluster_out = best_c;
+  return best_ctas;
+}
+
+// The q/k/v projection with what follows it in its epilogue: x[tokens, K] * w[features, K]^T,
+// features = (nh + 2 nkv) * d (nkv = 0 and no caches: queries only); each row times the factor
+// of the norm before it (row_partials, as in bf_qk_norm_rope_kv_write); q and k heads normed
+// (q_w, k_w: null for none) and turned (inv_freq: rot_half frequencies, a multiple of 32, or
+// null); q to q_out [tokens, nh * d], k and v into the pages at slots[t].  bn and cluster from
+// bf_gemm_cluster_qkv_plan.  Returns cudaErrorInvalidValue for what it does not take.
+BF_EXPORT int bf_gemm_bf16_cluster_qkv(
+    const void* x, const void* w, int tokens, int features, int K, long long ldx, long long ldw,
+    int bn, int cluster, const float* q_w, const float* k_w, const float* inv_freq, int rot_half,
+    const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache, int nh,
+    int nkv, int d, int page_size, long long num_slots, float eps, const float* row_partials,
+    int row_count, int row_width, float row_eps, int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (tokens > CL_MAX_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
+      ((uintptr_t)w & 15) || !q_out || !positions)
+    return (int)cudaErrorInvalidValue;
+  if (d <= 0 || d % 32 || d > 256 || bn <= 0 || bn > 256 || bn % d || cluster < 1 || cluster > 8 ||
+      nh <= 0 || nkv < 0 || features != (nh + 2 * nkv) * d)
+    return (int)cudaErrorInvalidValue;
+  if (inv_freq && (rot_half <= 0 || rot_half % 32 || 2 * rot_half > d))
+    return (int)cudaErrorInvalidValue;
+  if (nkv > 0 && (!k_cache || !v_cache || !slots || page_size <= 0))
+    return (int)cudaErrorInvalidValue;
+  // only arrangements whose clusters are all resident at once (the plan gives no other; one
+  // that needed a second wave, 24 clusters of 6, ended in a launch failure when it was tried)
+  if (resident_clusters(cluster) < (features + bn - 1) / bn) return (int)cudaErrorInvalidValue;
+  ClusterGemmParams p = {};
+  p.tokens = tokens;
+  p.features = features;
+  p.K = K;
+  p.bn = bn;
+  p.cluster = cluster;
+  p.err = err;
+  p.q_w = q_w;
+  p.k_w = k_w;
+  p.inv_freq = inv_freq;
+  p.rot_half = inv_freq ? rot_half : 0;
+  p.positions = positions;
+  p.slots = slots;
+  p.q_out = (__nv_bfloat16*)q_out;
+  p.k_cache = nkv > 0 ? (__nv_bfloat16*)k_cache : nullptr;
+  p.v_cache = nkv > 0 ? (__nv_bfloat16*)v_cache : nullptr;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.d = d;
+  p.page_size = page_size > 0 ? page_size : 1;
+  p.num_slots = num_slots;
+  p.head_eps = eps;
+  p.rs.partials = row_partials;
+  p.rs.count = row_count;
+  p.rs.inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
+  p.rs.eps = row_eps;
   return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
 }
 

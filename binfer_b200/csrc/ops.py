@@ -436,6 +436,59 @@ def gemm_bf16_cluster_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Te
     return xt, RowScale(partials, N, eps)
 
 
+def num_sms(device: torch.device) -> int:
+    sms = _num_sms.get(device.index)
+    if sms is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _num_sms[device.index] = sms
+    return sms
+
+
+def gemm_cluster_qkv_plan(features: int, K: int, d: int, device: torch.device,
+                          min_fill: float = 0.6):
+    """(bn, cluster, CTAs) for the q/k/v projection with the head norms, the rotation and the
+    store into the pages in its epilogue: the narrowest tile of whole heads whose clusters,
+    all resident at once, occupy ``min_fill`` of the SMs (or, if none does, the arrangement
+    with the most CTAs), or None where the kernel has no such arrangement."""
+    bn, c = _c_int(0), _c_int(0)
+    sms = num_sms(device)
+    n = lib().bf_gemm_cluster_qkv_plan(_c_int(features), _c_int(K), _c_int(d), _c_int(sms),
+                                       _c_int(max(1, int(min_fill * sms))), ctypes.byref(bn),
+                                       ctypes.byref(c))
+    return (bn.value, c.value, n) if n > 0 else None
+
+
+def gemm_bf16_cluster_qkv(x: torch.Tensor, w: torch.Tensor, q_w: Optional[torch.Tensor],
+                          k_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                          positions: torch.Tensor, slots: Optional[torch.Tensor],
+                          q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor], nh: int, nkv: int, d: int, eps: float,
+                          err: torch.Tensor, bn: int, cluster: int,
+                          row_scale: Optional[RowScale] = None) -> bool:
+    """``qk_norm_rope_kv_write(x @ w^T, ...)`` as one kernel for at most 64 token rows:
+    ``w`` is ``[(nh + 2 nkv) d, K]``, or ``[nh d, K]`` with no caches given (queries only).
+    Returns False, having done nothing, for what the kernel does not take."""
+    M, K = x.shape
+    writes = k_cache is not None
+    rot_half = 0 if inv_freq is None else inv_freq.numel()
+    if (M > CLUSTER_MAX_TOKENS or K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8
+            or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or d % 32 or d > 256
+            or rot_half % 32 or 2 * rot_half > d or not q_out.is_contiguous()
+            or w.shape[0] != (nh + (2 * nkv if writes else 0)) * d):
+        return False
+    if writes and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError("cache pages must be contiguous")
+    page_size = k_cache.shape[2] if writes else 1
+    num_slots = k_cache.shape[0] * page_size if writes else 0
+    _run("gemm_bf16_cluster_qkv", lib().bf_gemm_bf16_cluster_qkv, _ptr(x), _ptr(w), _c_int(M),
+         _c_int(w.shape[0]), _c_int(K), _c_ll(x.stride(0)), _c_ll(w.stride(0)), _c_int(bn),
+         _c_int(cluster), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _c_int(rot_half), _ptr(positions),
+         _ptr(slots if writes else None), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(nh),
+         _c_int(nkv if writes else 0), _c_int(d), _c_int(page_size), _c_ll(num_slots),
+         _c_float(eps), *_row_scale_args(row_scale, M), _ptr(err), _stream())
+    return True
+
+
 # -------------------------------------------------------------------- sampling
 def repetition_penalty(logits: torch.Tensor, items: torch.Tensor, penalty: torch.Tensor) -> None:
     """items: int32 [n, 3] of (row, token, count)."""

@@ -228,7 +228,8 @@ def step_timeline(a):
     events.sort()
     names = {1: "add_rmsnorm", 2: "silu_mul", 3: "qk_norm_rope", 4: "decode_attention",
              5: "attention_merge", 6: "gemm_cluster"}
-    phases = ["first block starts", "wait returns", "ends"]
+    phases = ["first block starts", "wait returns", "ends", "partial sums sent",
+              "cluster barrier passed", "products done"]
     t0 = prev = events[0][0]
     print(f"# decode step, batch {B}, context {ctx}, {a.layers} layers; microseconds", flush=True)
     for t, c in events:

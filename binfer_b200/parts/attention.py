@@ -15,6 +15,7 @@ An optional window restricts a query at p to keys in (p - window, p].
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -25,7 +26,16 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import (BuildEnv, DeferredLinear, EntryView, Mixer, StepContext, build_position,
                    register_mixer, split_scaled)
-from .linear import linear
+from .linear import cluster_token_limit, linear
+
+# BINFER_B200_FUSE_QKV=1: steps of few tokens run the q/k/v projection with the head norms,
+# the rotation and the store into the pages as one kernel.  Off unless asked for: its tiles
+# must be whole heads, which leaves the 8B shape 96 CTAs where the plain product has 128, and
+# inside a decode step that cost more (3.6 us) than the kernel it saves (8 layers, batch 8,
+# context 4096: 1.204 against 1.186 ms a step).
+FUSE_QKV = os.environ.get("BINFER_B200_FUSE_QKV", "0") != "0"
+# ... and only where those tiles give work to this share of the SMs
+FUSE_QKV_FILL = 0.6
 
 
 class GQAAttention(Mixer):
@@ -42,6 +52,7 @@ class GQAAttention(Mixer):
         self.position = (build_position(spec.position, spec.head_dim, env)
                          if spec.position is not None else None)
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self._qkv_plans = {}
 
     # ----------------------------------------------------------------- weights
     def param_specs(self) -> List[ParamSpec]:
@@ -53,6 +64,8 @@ class GQAAttention(Mixer):
         if s.qk_norm:
             specs += [ParamSpec(p + "q_norm.weight", (s.head_dim,), init="norm", role="vector"),
                       ParamSpec(p + "k_norm.weight", (s.head_dim,), init="norm", role="vector")]
+        if self.position is not None:
+            specs += self.position.param_specs(p)
         return specs
 
     def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
@@ -64,6 +77,8 @@ class GQAAttention(Mixer):
         if self.spec.qk_norm:
             self.q_norm = get(sp["q_norm.weight"])
             self.k_norm = get(sp["k_norm.weight"])
+        if self.position is not None:
+            self.position.load(get)
 
     # ------------------------------------------------------------------- cache
     def kv_need(self) -> Optional[KVNeed]:
@@ -83,21 +98,71 @@ class GQAAttention(Mixer):
         x, row_scale = split_scaled(x)
         s, T = self.spec, x.shape[0]
         g = view.group
-        if view.writes_cache:
-            qkv = linear(x, self.w_qkv)
-        else:       # the pages belong to another layer execution: only q is needed
-            qkv = linear(x, self.w_qkv[: self.q_size])
+        pos = self.position
         q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
-        ops.qk_norm_rope_kv_write(
-            qkv, self.q_norm, self.k_norm,
-            self.position.inv_freq if self.position is not None else None,
-            ctx.positions, ctx.slots[g] if view.writes_cache else None, q,
-            view.k_cache if view.writes_cache else None,
-            view.v_cache if view.writes_cache else None,
-            s.num_heads, s.num_kv_heads, s.head_dim, s.qk_norm_eps, ctx.err, row_scale=row_scale)
+        # the pages may belong to another layer execution: only q is needed then
+        w = self.w_qkv if view.writes_cache else self.w_qkv[: self.q_size]
+        if not self._project_fused(x, w, q, row_scale, ctx, view):
+            qkv = linear(x, w)
+            if pos is None or pos.inv_freq is not None:
+                # head norms, rotation and the store into the pages: one kernel
+                writes = view.writes_cache
+                ops.qk_norm_rope_kv_write(
+                    qkv, self.q_norm, self.k_norm, pos.inv_freq if pos is not None else None,
+                    ctx.positions, ctx.slots[g] if writes else None, q,
+                    view.k_cache if writes else None, view.v_cache if writes else None,
+                    s.num_heads, s.num_kv_heads, s.head_dim, s.qk_norm_eps, ctx.err,
+                    row_scale=row_scale)
+            else:
+                self._encode_unfused(qkv, q, row_scale, ctx, view)
         out = torch.empty_like(q)
         self.attend(q, out, ctx, view)
         return DeferredLinear(out, self.w_o)
+
+    def _project_fused(self, x, w, q, row_scale, ctx: StepContext, view: EntryView) -> bool:
+        """Few token rows in bfloat16: the projection, the head norms, the rotation and the
+        store into the pages as one kernel, where the split-K cluster product has a plan with
+        tiles of whole heads for this shape.  False, having done nothing, otherwise."""
+        s, pos = self.spec, self.position
+        if (not FUSE_QKV or x.dtype != torch.bfloat16 or x.shape[0] > cluster_token_limit()
+                or (pos is not None and pos.inv_freq is None)):
+            return False
+        key = (w.shape[0], w.shape[1])
+        if key not in self._qkv_plans:
+            self._qkv_plans[key] = ops.gemm_cluster_qkv_plan(*key, s.head_dim, x.device,
+                                                             max(FUSE_QKV_FILL, 0.6))
+        plan = self._qkv_plans[key]
+        if plan is None or plan[2] < FUSE_QKV_FILL * ops.num_sms(x.device):
+            return False
+        writes = view.writes_cache
+        return ops.gemm_bf16_cluster_qkv(
+            x, w, self.q_norm, self.k_norm, pos.inv_freq if pos is not None else None,
+            ctx.positions, ctx.slots[view.group] if writes else None, q,
+            view.k_cache if writes else None, view.v_cache if writes else None, s.num_heads,
+            s.num_kv_heads, s.head_dim, s.qk_norm_eps, ctx.err, *plan[:2], row_scale=row_scale)
+
+    def _encode_unfused(self, qkv, q, row_scale, ctx: StepContext, view: EntryView) -> None:
+        """A position encoding that is no rotation: the head norms write q, and k and v
+        into token-major scratch (a cache of one-token pages, token t in page t); the
+        encoding changes q and k there; a second pass stores k and v into the pages."""
+        s, T = self.spec, qkv.shape[0]
+        if not view.writes_cache:
+            qkv = torch.cat([qkv, qkv.new_zeros((T, 2 * self.kv_size))], dim=1)
+        k_rows = torch.empty((T, s.num_kv_heads, 1, s.head_dim), dtype=q.dtype, device=q.device)
+        v_rows = torch.empty_like(k_rows)
+        each = torch.arange(T, dtype=torch.int32, device=q.device)
+        ops.qk_norm_rope_kv_write(qkv, self.q_norm, self.k_norm, None, ctx.positions, each, q,
+                                  k_rows, v_rows, s.num_heads, s.num_kv_heads, s.head_dim,
+                                  s.qk_norm_eps, ctx.err, row_scale=row_scale)
+        self.position.apply(q.view(T, s.num_heads, s.head_dim),
+                            k_rows.view(T, s.num_kv_heads, s.head_dim), ctx.positions)
+        if view.writes_cache:
+            encoded = torch.cat([q, k_rows.view(T, self.kv_size), v_rows.view(T, self.kv_size)],
+                                dim=1)
+            ops.qk_norm_rope_kv_write(encoded, None, None, None, ctx.positions,
+                                      ctx.slots[view.group], q, view.k_cache, view.v_cache,
+                                      s.num_heads, s.num_kv_heads, s.head_dim, s.qk_norm_eps,
+                                      ctx.err)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext,
                view: EntryView) -> None:

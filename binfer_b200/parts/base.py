@@ -97,6 +97,36 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class PositionEncoding:
+    """How a token's absolute position enters an attention mixer's queries and keys.
+
+    Two forms, told apart by ``inv_freq``:
+
+    * the rotary family sets ``inv_freq`` (float32 ``[rot/2]`` on the device, ``rot`` at
+      most the head size): the pair ``(i, i + rot/2)`` of each query and key head turns by
+      ``position * inv_freq[i]`` inside the kernel that also norms the heads and stores the
+      keys.  Any table of frequencies goes this way (scaled, stretched, partial);
+    * every other encoding leaves ``inv_freq`` None and defines ``apply(q, k, positions)``,
+      which changes ``q [T, heads, d]`` and ``k [T, kv_heads, d]`` in place after the head
+      norms and before the keys are stored; the mixer then runs norm, ``apply`` and the
+      store as separate launches.
+
+    An encoding with tensors of its own names them in ``param_specs(prefix)`` (``prefix`` is
+    the mixer's) and takes them in ``load(get)``, like a part.
+    """
+
+    inv_freq: Optional[torch.Tensor] = None
+
+    def param_specs(self, prefix: str) -> List[ParamSpec]:
+        return []
+
+    def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
+        pass
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     """Per-token transformation ``[T, H] -> [T, H]`` (dense here; experts elsewhere)."""
 
@@ -227,7 +257,7 @@ def register_norm(kind: str, factory: Callable) -> None:
 
 
 def register_position(kind: str, factory: Callable) -> None:
-    """``factory(spec, head_dim, env) -> position encoding``"""
+    """``factory(spec, head_dim, env) -> PositionEncoding``"""
     _POSITIONS[kind] = factory
 
 

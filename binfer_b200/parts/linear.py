@@ -53,6 +53,13 @@ def _use_cluster(M: int, N: int, K: int) -> bool:
     return N <= (8192 if _POLICY == "auto" else 32768) and (K >= 2048 or _POLICY == "own")
 
 
+def cluster_token_limit() -> int:
+    """Most token rows for which the policy sends products to the split-K cluster kernel."""
+    if _POLICY == "library":
+        return 0
+    return 16 if _POLICY == "auto" else ops.CLUSTER_MAX_TOKENS
+
+
 _plans = {}
 
 

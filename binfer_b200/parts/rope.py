@@ -14,10 +14,10 @@ from __future__ import annotations
 import torch
 
 from ..config.specs import RopeSpec
-from .base import BuildEnv, register_position
+from .base import BuildEnv, PositionEncoding, register_position
 
 
-class RotaryEncoding:
+class RotaryEncoding(PositionEncoding):
     """Holds ``inv_freq`` (float32 ``[rot/2]``) for the qkv post-processing kernel."""
 
     def __init__(self, spec: RopeSpec, head_dim: int, env: BuildEnv):

@@ -319,6 +319,88 @@ def test_gemm_cluster_adds_into_the_stream_and_prepares_the_norm(cuda_device, M,
     _close(out, gd[:, :I] / (1 + torch.exp(-gd[:, :I])) * gd[:, I:], BF16)
 
 
+@pytest.mark.parametrize("T,nh,nkv,d,rot,K,bn,c,norm,scaled", [
+    (8, 32, 8, 128, 128, 4096, 128, 2, True, True),      # the 8B decode step's arrangement
+    (5, 6, 2, 64, 64, 1024, 128, 2, True, False),        # two heads a tile
+    (13, 5, 1, 96, 64, 1280, 192, 4, True, True),        # a rotation over part of the head
+    (16, 3, 3, 256, 256, 512, 256, 1, False, False),     # one CTA a tile, no head norms
+    (37, 7, 1, 128, 0, 2304, 128, 5, True, True),        # token rows beyond 32, no rotation
+    (2, 4, 0, 128, 128, 640, 256, 2, True, False),       # queries only: another layer's pages
+    (1, 8, 2, 32, 0, 768, 32, 3, False, True),           # fewer tokens than CTAs in a cluster
+])
+def test_gemm_cluster_qkv_norms_turns_and_stores(cuda_device, T, nh, nkv, d, rot, K, bn, c, norm,
+                                                 scaled):
+    """The q/k/v projection with its epilogue against the product followed by the plain
+    head norm, rotation and store: q, and every page slot of k and v (untouched slots
+    stay zero, a token with a negative slot is not stored)."""
+    from binfer_b200.csrc import ops
+    dev, ps, eps, theta = cuda_device, 4, 1e-5, 5000.0
+    pages = -(-T // ps) + 3
+    g = torch.Generator().manual_seed(T * 1000 + K)
+    x = torch.randn(T, K, generator=g).to(BF16).to(dev)
+    w = (torch.randn((nh + 2 * nkv) * d, K, generator=g) / math.sqrt(K)).to(BF16).to(dev)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(dev) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(dev) if norm else None
+    pos = torch.randint(0, 3000, (T,), generator=g).to(torch.int32).to(dev)
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32).to(dev)
+    if T > 3:
+        slots[3] = -1
+    inv = None
+    if rot:
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        inv = (theta ** (-2.0 * i / rot)).float().to(dev)
+    scale = None
+    factor = torch.ones(T, dtype=torch.float64)
+    if scaled:
+        partials = (torch.rand(T, 37, generator=g) * 40).to(dev)
+        scale = ops.RowScale(partials, 1536, 1e-6)
+        factor = scale.factors().double().cpu()
+    kc = torch.zeros(pages, max(nkv, 1), ps, d, device=dev, dtype=BF16) if nkv else None
+    vc = torch.zeros_like(kc) if nkv else None
+    q_out = torch.empty(T, nh * d, device=dev, dtype=BF16)
+    err = _err(dev)
+    assert ops.gemm_bf16_cluster_qkv(x, w, qw, kw, inv, pos, slots if nkv else None, q_out, kc, vc,
+                                     nh, nkv, d, eps, err, bn, c, row_scale=scale)
+    assert int(err.item()) == 0
+    y = (x.double().cpu() @ w.double().cpu().T) * factor[:, None]
+    q = y[:, :nh * d].view(T, nh, d)
+    k = y[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+    v = y[:, (nh + nkv) * d:].view(T, nkv, d)
+    if norm:
+        q = P.rms_norm(q, qw.double().cpu(), eps)
+        k = P.rms_norm(k, kw.double().cpu(), eps) if nkv else k
+    if rot:
+        ang = P.rope_angles(pos.cpu(), rot, theta)
+        q = P.apply_rope(q, ang)
+        k = P.apply_rope(k, ang) if nkv else k
+    _close(q_out.view(T, nh, d), q, BF16)
+    if not nkv:
+        return
+    stored = 0
+    for t in range(T):
+        s_ = int(slots[t])
+        if s_ < 0:
+            continue
+        stored += 1
+        _close(kc[s_ // ps, :, s_ % ps], k[t], BF16)
+        _close(vc[s_ // ps, :, s_ % ps], v[t], BF16)
+    assert int(kc.abs().sum(dim=(1, 3)).flatten().count_nonzero()) == stored
+    assert int(vc.abs().sum(dim=(1, 3)).flatten().count_nonzero()) == stored
+
+
+def test_gemm_cluster_qkv_plan_keeps_whole_heads(cuda_device):
+    from binfer_b200.csrc import ops
+    sms = ops.num_sms(cuda_device)
+    for features, K, d in [(6144, 4096, 128), (2560, 1536, 128), (10240, 5120, 128),
+                           (1536, 1024, 64), (1280, 2048, 256), (480, 640, 96)]:
+        plan = ops.gemm_cluster_qkv_plan(features, K, d, cuda_device)
+        assert plan is not None, (features, K, d)
+        bn, c, ctas = plan
+        assert bn % d == 0 and bn <= 256 and 1 <= c <= 8 and (K // 64) // c >= 4
+        assert ctas == -(-features // bn) * c <= sms
+    assert ops.gemm_cluster_qkv_plan(4096, 4096, 80, cuda_device) is None     # not whole warps
+
+
 # ------------------------------------------------------------------------ sampling
 def _sample(dev, logits, temperature, top_k=0, top_p=1.0, u=0.0):
     from binfer_b200.csrc import ops

@@ -252,6 +252,134 @@ def test_toy_mixer_with_state_and_routed_ffn(cuda_device):
     assert torch.equal(runner.step([StepItem("b", toks, [22])]), first)
 
 
+@dataclass(frozen=True)
+class StretchedRotarySpec:
+    """Rotations with frequencies base * (i + 1) over the first ``rotary_dim`` features."""
+    kind: str = "test_stretched_rotary"
+    base: float = 0.03
+    rotary_dim: int = 8
+
+
+@dataclass(frozen=True)
+class BucketShiftSpec:
+    """A learned vector per bucket of ``width`` positions, added to every q and k head."""
+    kind: str = "test_bucket_shift"
+    buckets: int = 6
+    width: int = 3
+
+
+def _register_toy_positions():
+    from binfer_b200.parts import PositionEncoding, register_position
+    from binfer_b200.weights import ParamSpec
+
+    class StretchedRotary(PositionEncoding):
+        def __init__(self, spec, head_dim, env):
+            i = torch.arange(spec.rotary_dim // 2, dtype=torch.float32)
+            self.inv_freq = (spec.base * (i + 1)).to(env.device)
+
+    class BucketShift(PositionEncoding):
+        def __init__(self, spec, head_dim, env):
+            self.spec, self.head_dim = spec, head_dim
+
+        def param_specs(self, prefix):
+            self.table_spec = ParamSpec(prefix + "position_table.weight",
+                                        (self.spec.buckets, self.head_dim))
+            return [self.table_spec]
+
+        def load(self, get):
+            self.table = get(self.table_spec)
+
+        def apply(self, q, k, positions):
+            b = (positions.long() // self.spec.width).clamp(max=self.spec.buckets - 1)
+            shift = self.table[b].to(q.dtype)[:, None, :]
+            q.add_(shift)
+            k.add_(shift)
+
+    register_position("test_stretched_rotary", StretchedRotary)
+    register_position("test_bucket_shift", BucketShift)
+
+
+# (the bounds of the replay tests: largest difference and root mean square, over the logits')
+@pytest.mark.parametrize("dtype,tol,tol_rms", [(torch.float32, 2e-5, 5e-6),
+                                               (torch.bfloat16, 3e-2, 1e-2)])
+def test_toy_position_encodings(cuda_device, dtype, tol, tol_rms):
+    """Two position encodings that the framework does not ship, registered here: a rotation
+    with another table of frequencies (it runs inside the fused kernel) and an additive one
+    with a tensor of its own (it runs between the head norms and the store).  A third layer
+    execution reads the second one's pages, so that the encoding meets a mixer that stores
+    nothing.  Whole and in portions, against a plain restatement."""
+    from binfer_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, NormSpec,
+                                    ScheduleEntry)
+    from binfer_b200.engine import make_runner
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.parts import build_model, param_specs_for
+    from binfer_b200.weights import TensorSource, random_tensors
+    _register_toy_positions()
+    norm = NormSpec(eps=1e-6)
+    stretched, shift = StretchedRotarySpec(), BucketShiftSpec()
+    layers = [LayerSpec(mixer=AttentionSpec(num_heads=4, num_kv_heads=2, head_dim=16,
+                                            position=stretched),
+                        ffn=GatedMLPSpec(intermediate_size=24), norm=norm),
+              LayerSpec(mixer=AttentionSpec(num_heads=4, num_kv_heads=1, head_dim=16, qk_norm=True,
+                                            position=shift),
+                        ffn=GatedMLPSpec(intermediate_size=40), norm=norm)]
+    sched = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1, cache_from=1)]
+    spec = _toy_spec(layers, sched, vocab=40, hidden=32)
+    names = [s.name for s in param_specs_for(spec)]
+    assert "model.layers.1.self_attn.position_table.weight" in names
+    assert "model.layers.0.self_attn.position_table.weight" not in names
+    env = _env(dtype)
+    # (weights small enough that the scores stay of order one: with a sharp softmax the
+    # bfloat16 rounding of this 32-wide model alone exceeds the bounds)
+    weights = random_tensors(param_specs_for(spec), seed=9, std=0.1, norm_std=0.05)
+    model = build_model(spec, env, TensorSource.from_dict(weights))
+    n = 19
+    toks = H.random_tokens(n, 40, 5)
+
+    w = {k: v.double() for k, v in weights.items()}
+    if dtype == torch.bfloat16:
+        w = {k: v.to(torch.bfloat16).double() for k, v in w.items()}
+    pos = torch.arange(n)
+    x = P.embedding(torch.tensor(toks), w["model.embed_tokens.weight"])
+    kept = {}
+    for e, entry in enumerate(sched):
+        p = f"model.layers.{entry.layer}."
+        a, m = p + "self_attn.", layers[entry.layer].mixer
+        h = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6)
+        q = (h @ w[a + "q_proj.weight"].T).view(n, m.num_heads, 16)
+        k = (h @ w[a + "k_proj.weight"].T).view(n, m.num_kv_heads, 16)
+        v = (h @ w[a + "v_proj.weight"].T).view(n, m.num_kv_heads, 16)
+        if m.qk_norm:
+            q = P.rms_norm(q, w[a + "q_norm.weight"], 1e-6)
+            k = P.rms_norm(k, w[a + "k_norm.weight"], 1e-6)
+        if entry.layer == 0:
+            i = torch.arange(stretched.rotary_dim // 2, dtype=torch.float32)
+            ang = pos.float()[:, None] * (stretched.base * (i + 1))[None, :]
+            q, k = P.apply_rope(q, ang), P.apply_rope(k, ang)
+        else:
+            b = (pos // shift.width).clamp(max=shift.buckets - 1)
+            add = w[a + "position_table.weight"][b][:, None, :]
+            q, k = q + add, k + add
+        kept[e] = (k, v)
+        if entry.cache_from is not None:
+            k, v = kept[entry.cache_from]
+        att = P.causal_attention(q, k, v, 16 ** -0.5).reshape(n, -1) @ w[a + "o_proj.weight"].T
+        x = x + att
+        h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6)
+        x = x + P.swiglu_mlp(h, w, p + "mlp.")
+    want = P.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+    for cuts in ([n], [6, 1, 2, 10]):
+        runner = make_runner(model, env, page_size=4, num_pages=8, max_requests=2)
+        runner.add_request("r")
+        rows, at = [], 0
+        for c in cuts:
+            rows.append(runner.step([StepItem("r", toks[at:at + c], list(range(c)))]).clone())
+            at += c
+        got = torch.cat(rows).float().cpu()
+        assert H.rel_err(got, want) < tol and H.rel_rms(got, want) < tol_rms, cuts
+
+
 def test_schedule_runs_a_layer_twice_and_shares_pages(cuda_device):
     """The order of execution is data: layer 0 runs twice (two caches of its own), and the
     last entry reads the pages that the first one wrote."""

@@ -191,6 +191,40 @@ def test_replay_with_products_that_prepare_the_next_norm(cuda_device, plain_logi
     assert worst <= TOL[dtype], f"fused and unfused steps differ by {worst:.3g}"
 
 
+@pytest.mark.parametrize("which", ["F", "O", "V", "M"])
+@pytest.mark.parametrize("regime", ["tail", "mixed"])
+def test_replay_with_the_projection_that_stores_into_the_pages(cuda_device, plain_logits, regime,
+                                                               which):
+    """Steps of few tokens run the q/k/v projection with the head norms, the rotation and the
+    store into the pages in its epilogue (switched on here, also where its tiles would leave
+    most SMs idle).  Same logits as the plain implementation, and (to bfloat16 rounding) as the
+    same steps with the separate kernels; V has windows, whose pages are given back."""
+    from binfer_b200.csrc import ops
+    import importlib
+    att = importlib.import_module("binfer_b200.parts.attention")
+    dtype = torch.bfloat16
+    reqs = _requests(which, (55, 61) if regime == "mixed" else ())
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    steps = {"tail": H.trace_decode_tail, "mixed": H.trace_mixed}[regime](reqs)
+    ps = H.TINY[which]["page_size"]
+    outs = []
+    before = att.FUSE_QKV, att.FUSE_QKV_FILL
+    for fuse in (True, False):
+        att.FUSE_QKV, att.FUSE_QKV_FILL = fuse, 0.0
+        seen = _Names()
+        ops.set_profiler(seen)
+        try:
+            got = H.run_trace(_runner(model_dir, dtype, ps, H.peak_pages(steps, ps)), steps)
+        finally:
+            ops.set_profiler(None)
+            att.FUSE_QKV, att.FUSE_QKV_FILL = before
+        assert ("gemm_bf16_cluster_qkv" in seen.names) == fuse
+        _compare(got, ref, dtype, f"{which}/{regime}/fused={fuse}")
+        outs.append(got)
+    worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
+    assert worst <= TOL[dtype], f"fused and separate kernels differ by {worst:.3g}"
+
+
 def test_long_context_bfloat16(cuda_device, plain_logits):
     """A prompt of 2600 tokens (portions of 2048 and the rest), then 40 tokens one by one: the
     tcgen05 prefill kernels over many key tiles, the decode kernels over 21 splits, and the
