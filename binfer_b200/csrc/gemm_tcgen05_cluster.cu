@@ -73,6 +73,14 @@ struct ClusterGemmParams {
   long long num_slots;
   float head_eps;
   BfRowScale rs;                // factor on the rows of the product (the norm before it)
+  // Fused SwiGLU of the stacked gate/up projection (act_out != null; one CTA a tile, no
+  // split of K): w is [2 inter, K], gate rows first; the tile's first bn/2 weight rows are
+  // the gate rows of outputs tile * bn/2 .., the others the up rows of the same outputs, so
+  // that one accumulator holds both; act_out[t, o] = silu(f g) * (f u), f the row's factor
+  // (rs), goes from tensor memory to global memory with no pass through shared memory.
+  __nv_bfloat16* act_out;
+  long long ldact;
+  int inter;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -128,6 +136,21 @@ __device__ __forceinline__ void rotate_pairs(float (&v)[8], const QkvToken& k) {
   }
 }
 
+// One stage's weight rows: the tile's bn rows, or (SwiGLU form) bn/2 gate rows and the bn/2
+// up rows of the same outputs, one behind the other (bn/2 is a multiple of 8, so the second
+// box starts on a swizzle period).
+__device__ __forceinline__ void load_weights(const ClusterGemmParams& p, const CUtensorMap* map_w,
+                                             uint8_t* dst, uint64_t* bar, int k, int tile) {
+  if (!p.act_out) {
+    tma_load_2d(dst, map_w, bar, k, tile * p.bn);
+  } else {
+    const int h = p.bn / 2;
+    tma_load_2d(dst, map_w, bar, k, tile * h);
+    tma_load_2d(dst + (size_t)h * BK * 2, map_w, bar, k, p.inter + tile * h);
+  }
+}
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
 template <typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -146,8 +169,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   float* recv = reinterpret_cast<float*>(base + CL_BAR_BYTES);
   const int slice = p.bn / p.cluster;                          // columns owned per CTA
   const int own_tokens = (p.tokens + p.cluster - 1) / p.cluster;   // (q/k/v form) per CTA
-  const int recv_bytes = p.q_out ? p.cluster * own_tokens * p.bn * 4
-                                 : p.cluster * p.tok_rows * slice * 4;
+  const int recv_bytes = p.act_out ? 0
+                         : p.q_out ? p.cluster * own_tokens * p.bn * 4
+                                   : p.cluster * p.tok_rows * slice * 4;
   uint8_t* tiles = base + CL_BAR_BYTES + ((recv_bytes + 1023) & ~1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -189,8 +213,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   if (warp == 2 && lane == 0) {
     for (int i = 0; i < pre; ++i) {
       mbar_expect_tx(full + i, stage_bytes);
-      tma_load_2d(tiles + (size_t)i * stage_bytes + a_bytes, &map_w, full + i, (kc0 + i) * BK,
-                  tile * p.bn);
+      load_weights(p, &map_w, tiles + (size_t)i * stage_bytes + a_bytes, full + i, (kc0 + i) * BK,
+                   tile);
     }
   }
   bf_pdl_wait();
@@ -207,7 +231,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         uint8_t* dst = tiles + (size_t)stage * stage_bytes;
         mbar_expect_tx(full + stage, stage_bytes);
         tma_load_2d(dst, &map_x, full + stage, kc * BK, 0);
-        tma_load_2d(dst + a_bytes, &map_w, full + stage, kc * BK, tile * p.bn);
+        load_weights(p, &map_w, dst + a_bytes, full + stage, kc * BK, tile);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
@@ -247,15 +271,68 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     // than 32 token rows) reads lanes 32..63.  A lane holds one token's row of the partial sum.
     const int row = (warp == 5 ? 32 : 0) + lane;
     const uint32_t lanes = (uint32_t)(warp == 5 ? 32 : 0) << 16;
-    const int chunks = p.bn / 16, half = (chunks + 1) / 2;
-    const int c_begin = warp == 4 ? half * 16 : 0, c_end = warp == 0 ? half * 16 : p.bn;
+    const int width = p.act_out ? p.bn / 2 : p.bn;          // columns to walk: outputs or sums
+    const int chunks = (width + 15) / 16, half = (chunks + 1) / 2;
+    const int c_begin = warp == 4 ? half * 16 : 0, c_end = warp == 0 ? half * 16 : chunks * 16;
+    // (SwiGLU form) the factor of this lane's row, worked out while the products run
+    float factor = 1.f;
+    if (p.act_out && p.rs.partials)
+      for (int t = (warp == 5 ? 32 : 0); t < p.tokens && t < (warp == 5 ? 64 : 32); ++t) {
+        const float ft = bf_row_factor(p.rs, t, lane);
+        if (t == row) factor = ft;
+      }
     bool have = kc1 > kc0;
     if (have) have = mbar_wait(acc_full, 0, abort);
     have = __all_sync(0xffffffffu, have);
     tc_fence_after();
     BF_TRACE_POINT(10 * BF_TR_GEMM + 5);
     const uint32_t my_recv = smem_u32(recv);
-    for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+    for (int c0 = c_begin; c0 < c_end && p.act_out; c0 += 16) {
+      // gate columns c0.., up columns bn/2 + c0.. of both issuers' accumulators
+      const int h = p.bn / 2;
+      uint32_t g[16], u[16];
+      if (have) {
+        const uint32_t at = tmem_base + lanes + (uint32_t)c0;
+        if (p.issuers == 2 && kc1 - kc0 >= 2) {
+          uint32_t g2[16], u2[16];
+          tmem_ld16_pair(at, at + (uint32_t)p.acc_stride, g, g2);
+          tmem_ld16_pair(at + (uint32_t)h, at + (uint32_t)(p.acc_stride + h), u, u2);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            g[j] = __float_as_uint(__uint_as_float(g[j]) + __uint_as_float(g2[j]));
+            u[j] = __float_as_uint(__uint_as_float(u[j]) + __uint_as_float(u2[j]));
+          }
+        } else {
+          tmem_ld16_pair(at, at + (uint32_t)h, g, u);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;   // a timeout (flagged): zeros
+      }
+      if (row < p.tokens) {
+        const int o0 = tile * h + c0;                     // first output of the chunk
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float a = silu_fast(__uint_as_float(g[2 * j]) * factor) *
+                          (__uint_as_float(u[2 * j]) * factor);
+          const float b = silu_fast(__uint_as_float(g[2 * j + 1]) * factor) *
+                          (__uint_as_float(u[2 * j + 1]) * factor);
+          packed[j] = pack_bf16x2(__float_as_uint(a), __float_as_uint(b));
+        }
+        __nv_bfloat16* dst = p.act_out + (size_t)row * p.ldact + o0;
+        if (c0 + 16 <= h && o0 + 16 <= p.inter) {         // (16-byte aligned: o0 and ldact are multiples of 8)
+          reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < h && o0 + j < p.inter)
+              dst[j] = reinterpret_cast<const __nv_bfloat16*>(packed)[j];
+        }
+      }
+    }
+    for (int c0 = c_begin; c0 < c_end && !p.act_out; c0 += 16) {
       uint32_t r[16];
       if (have) {
         if (p.issuers == 2 && kc1 - kc0 >= 2) {          // with the second issuer's share
@@ -305,7 +382,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // The fused epilogue's inputs do not depend on the product: those of a thread's first item
   // are asked for before the cluster waits for its slowest member (further items' later).
   const int groups = slice / 4;
-  const int n_plain = p.q_out ? 0 : p.tokens * groups;
+  const int n_plain = p.q_out || p.act_out ? 0 : p.tokens * groups;
   float pre_r[4] = {0.f, 0.f, 0.f, 0.f}, pre_w[4] = {0.f, 0.f, 0.f, 0.f};
   if (p.resid && (int)threadIdx.x < n_plain) {
     const int g = threadIdx.x / p.tokens, t = threadIdx.x - g * p.tokens;
@@ -456,12 +533,14 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   p.tok_rows = p.tokens <= 16 ? 16 : p.tokens <= 32 ? 32 : 64;
   int e = bf_make_tensor_map_bf16_2d(&mx, x, p.tokens, p.K, ldx, p.tok_rows, BK);
   if (e) return e;
-  e = bf_make_tensor_map_bf16_2d(&mw, w, p.features, p.K, ldw, p.bn, BK);
+  e = bf_make_tensor_map_bf16_2d(&mw, w, p.features, p.K, ldw, p.act_out ? p.bn / 2 : p.bn, BK);
   if (e) return e;
   const size_t smem_max = 226 * 1024;
   const size_t stage_bytes = (size_t)(p.tok_rows + p.bn) * BK * 2;
   const size_t recv_rows =
-      p.q_out ? (size_t)p.cluster * ((p.tokens + p.cluster - 1) / p.cluster) : (size_t)p.tok_rows;
+      p.act_out ? 0
+      : p.q_out ? (size_t)p.cluster * ((p.tokens + p.cluster - 1) / p.cluster)
+                : (size_t)p.tok_rows;
   const size_t recv_bytes = (recv_rows * p.bn * 4 + 1023) & ~(size_t)1023;
   // behind the last stage the MMA still reads 128 token rows' worth of shared memory
   const size_t fixed = 1024 + CL_BAR_BYTES + recv_bytes + 16 * 1024;
@@ -725,6 +804,49 @@ BF_EXPORT int bf_gemm_bf16_cluster_qkv(
   p.page_size = page_size > 0 ? page_size : 1;
   p.num_slots = num_slots;
   p.head_eps = eps;
+  p.rs.partials = row_partials;
+  p.rs.count = row_count;
+  p.rs.inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
+  p.rs.eps = row_eps;
+  return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
+}
+
+// Tile for the SwiGLU form: the narrowest tile (bn = 2 h weight rows for h outputs, h a multiple
+// of 8, bn at most 256) that gives every output a CTA in one wave.  Returns the number of
+// CTAs, or 0 where there is none (more than 128 outputs an SM).
+BF_EXPORT int bf_gemm_swiglu_plan(int inter, int K, int num_sms, int* bn_out) {
+  if (inter <= 0 || num_sms <= 0 || (K + BK - 1) / BK < 4) return 0;
+  int h = (inter + num_sms - 1) / num_sms;
+  h = (h + 7) / 8 * 8;
+  if (h < 16) h = 16;
+  if (2 * h > 256) return 0;
+  *bn_out = 2 * h;
+  return (inter + h - 1) / h;
+}
+
+// act[tokens, inter] = silu(f g) * (f u) with [g | u] = x[tokens, K] * w[2 inter, K]^T (gate
+// rows first) and f the factor of the norm before the projection (row_partials as in
+// bf_silu_mul_scaled; null: 1), as one kernel for at most 64 token rows.  bn from
+// bf_gemm_swiglu_plan.  Returns cudaErrorInvalidValue for what it does not take.
+BF_EXPORT int bf_gemm_bf16_swiglu(const void* x, const void* w, int tokens, int inter, int K,
+                                  long long ldx, long long ldw, int bn, void* act,
+                                  long long ldact, const float* row_partials, int row_count,
+                                  int row_width, float row_eps, int* err, cudaStream_t stream) {
+  if (tokens <= 0 || inter <= 0) return 0;
+  if (tokens > CL_MAX_TOKENS || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) ||
+      ((uintptr_t)w & 15) || !act || ((uintptr_t)act & 15) || ldact % 8)
+    return (int)cudaErrorInvalidValue;
+  if (bn < 32 || bn > 256 || bn % 16) return (int)cudaErrorInvalidValue;
+  ClusterGemmParams p = {};
+  p.tokens = tokens;
+  p.features = 2 * inter;
+  p.K = K;
+  p.bn = bn;
+  p.cluster = 1;
+  p.err = err;
+  p.act_out = (__nv_bfloat16*)act;
+  p.ldact = ldact;
+  p.inter = inter;
   p.rs.partials = row_partials;
   p.rs.count = row_count;
   p.rs.inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;

@@ -489,6 +489,33 @@ def gemm_bf16_cluster_qkv(x: torch.Tensor, w: torch.Tensor, q_w: Optional[torch.
     return True
 
 
+def gemm_swiglu_plan(inter: int, K: int, device: torch.device):
+    """bn for ``gemm_bf16_swiglu``, or None where its tiles would not fit one wave."""
+    bn = _c_int(0)
+    n = lib().bf_gemm_swiglu_plan(_c_int(inter), _c_int(K), _c_int(num_sms(device)),
+                                  ctypes.byref(bn))
+    return bn.value if n > 0 else None
+
+
+def gemm_bf16_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
+                     err: torch.Tensor, bn: int, row_scale: Optional[RowScale] = None) -> bool:
+    """``silu_mul(x @ w_gate_up^T)`` as one kernel for at most 64 token rows: ``w_gate_up`` is
+    ``[2 I, K]`` with the gate rows first, ``out`` is ``[M, I]``.  Returns False, having done
+    nothing, for what the kernel does not take."""
+    M, K = x.shape
+    I = out.shape[1]
+    if (M > CLUSTER_MAX_TOKENS or K % 8 or x.stride(1) != 1 or w_gate_up.stride(1) != 1
+            or x.stride(0) % 8 or w_gate_up.stride(0) % 8 or x.data_ptr() % 16
+            or w_gate_up.data_ptr() % 16 or out.stride(1) != 1 or out.stride(0) % 8
+            or out.data_ptr() % 16 or w_gate_up.shape[0] != 2 * I or out.shape[0] != M
+            or out.dtype != torch.bfloat16):
+        return False
+    _run("gemm_bf16_swiglu", lib().bf_gemm_bf16_swiglu, _ptr(x), _ptr(w_gate_up), _c_int(M),
+         _c_int(I), _c_int(K), _c_ll(x.stride(0)), _c_ll(w_gate_up.stride(0)), _c_int(bn),
+         _ptr(out), _c_ll(out.stride(0)), *_row_scale_args(row_scale, M), _ptr(err), _stream())
+    return True
+
+
 # -------------------------------------------------------------------- sampling
 def repetition_penalty(logits: torch.Tensor, items: torch.Tensor, penalty: torch.Tensor) -> None:
     """items: int32 [n, 3] of (row, token, count)."""

@@ -50,7 +50,12 @@ def _use_cluster(M: int, N: int, K: int) -> bool:
         return False
     # wider weights (the gate/up projection, on "clusters" of one CTA) measured 2 us slower
     # per call than the library inside a decode step
-    return N <= (8192 if _POLICY == "auto" else 32768) and (K >= 2048 or _POLICY == "own")
+    return N <= (_CLUSTER_MAX_FEATURES if _POLICY == "auto" else 32768) and (
+        K >= 2048 or _POLICY == "own")
+
+
+# widest weight (output features) that goes to the cluster kernel under "auto"
+_CLUSTER_MAX_FEATURES = int(os.environ.get("BINFER_B200_CLUSTER_MAX_FEATURES", "8192"))
 
 
 def cluster_token_limit() -> int:

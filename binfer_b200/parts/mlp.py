@@ -7,6 +7,7 @@ activation kernel reads both halves of each output row.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List
 
 import torch
@@ -16,7 +17,10 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import (BuildEnv, DeferredLinear, FeedForward, ScaledRows, StepContext, register_ffn,
                    split_scaled)
-from .linear import linear
+from .linear import cluster_token_limit, linear
+
+# BINFER_B200_FUSE_SWIGLU=0: the stacked gate/up projection and the activation as two kernels
+FUSE_SWIGLU = os.environ.get("BINFER_B200_FUSE_SWIGLU", "1") != "0"
 
 
 class GatedMLP(FeedForward):
@@ -28,6 +32,7 @@ class GatedMLP(FeedForward):
         self.spec, self.hidden, self.prefix, self.env = spec, hidden_size, prefix, env
         self.inter = spec.intermediate_size
         self.w_gate_up = self.w_down = None
+        self._swiglu_bn = None
 
     def param_specs(self) -> List[ParamSpec]:
         p = self.prefix
@@ -50,10 +55,25 @@ class GatedMLP(FeedForward):
         if isinstance(x, ScaledRows) and (self.inter % 8 or self.inter < 256):
             x = x.dense()                  # the activation kernel takes the factor at other sizes only
         x, row_scale = split_scaled(x)
-        gu = linear(x, self.w_gate_up)
         h = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gu, h, row_scale=row_scale)
+        if not self._project_fused(x, h, row_scale):
+            gu = linear(x, self.w_gate_up)
+            ops.silu_mul(gu, h, row_scale=row_scale)
         return DeferredLinear(h, self.w_down)
+
+    def _project_fused(self, x, h, row_scale) -> bool:
+        """Few token rows in bfloat16: the stacked projection with the activation in its
+        epilogue, one CTA a tile of gate rows and the up rows of the same outputs.  False,
+        having done nothing, where that kernel does not run."""
+        if (not FUSE_SWIGLU or x.dtype != torch.bfloat16 or x.shape[0] > cluster_token_limit()
+                or self.inter % 8):
+            return False
+        if self._swiglu_bn is None:
+            self._swiglu_bn = ops.gemm_swiglu_plan(self.inter, x.shape[1], x.device) or 0
+        if not self._swiglu_bn:
+            return False
+        return ops.gemm_bf16_swiglu(x, self.w_gate_up, h, ops.error_word(x.device),
+                                    self._swiglu_bn, row_scale=row_scale)
 
 
 register_ffn("gated_mlp", GatedMLP)

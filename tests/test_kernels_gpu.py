@@ -401,6 +401,36 @@ def test_gemm_cluster_qkv_plan_keeps_whole_heads(cuda_device):
     assert ops.gemm_cluster_qkv_plan(4096, 4096, 80, cuda_device) is None     # not whole warps
 
 
+@pytest.mark.parametrize("T,I,K,bn,scaled", [
+    (8, 12288, 4096, 0, True),        # the 8B decode step's shape, the plan's tile
+    (5, 1000, 512, 0, False),         # outputs that are no multiple of the tile
+    (16, 2504, 320, 48, True),        # 24 outputs a tile: the last chunk of a tile is cut
+    (37, 264, 1024, 256, True),       # token rows beyond 32; one tile holds part of the outputs
+    (1, 4480, 1536, 112, False),
+])
+def test_gemm_swiglu_matches_product_then_activation(cuda_device, T, I, K, bn, scaled):
+    """silu(f g) * (f u) of the stacked gate/up product, straight from tensor memory."""
+    from binfer_b200.csrc import ops
+    dev = cuda_device
+    g = torch.Generator().manual_seed(I + K + T)
+    x = torch.randn(T, K, generator=g).to(BF16).to(dev)
+    w = (2.0 * torch.randn(2 * I, K, generator=g) / math.sqrt(K)).to(BF16).to(dev)
+    scale, f = None, torch.ones(T, dtype=torch.float64)
+    if scaled:
+        scale = ops.RowScale((torch.rand(T, 130, generator=g) * 8).to(dev), 512, 1e-6)
+        f = scale.factors().double().cpu()
+    if bn == 0:
+        bn = ops.gemm_swiglu_plan(I, K, dev)
+        assert bn and bn % 16 == 0 and -(-I // (bn // 2)) <= ops.num_sms(dev)
+    out = torch.full((T, I), 7.0, device=dev, dtype=BF16)
+    err = _err(dev)
+    assert ops.gemm_bf16_swiglu(x, w, out, err, bn, row_scale=scale)
+    assert int(err.item()) == 0
+    y = (x.double().cpu() @ w.double().cpu().T) * f[:, None]
+    gate, up = y[:, :I], y[:, I:]
+    _close(out, gate / (1 + torch.exp(-gate)) * up, BF16)
+
+
 # ------------------------------------------------------------------------ sampling
 def _sample(dev, logits, temperature, top_k=0, top_p=1.0, u=0.0):
     from binfer_b200.csrc import ops

@@ -183,8 +183,8 @@ def test_replay_with_products_that_prepare_the_next_norm(cuda_device, plain_logi
             ops.set_profiler(None)
             lin.FUSE_NORM = True
         assert ("gemm_bf16_cluster_add_norm" in seen.names) == fuse
-        if fuse:
-            assert "silu_mul_scaled" in seen.names
+        if fuse:        # the factor is applied by what follows the next product
+            assert "silu_mul_scaled" in seen.names or "gemm_bf16_swiglu" in seen.names
         _compare(got, ref, dtype, f"{which}/{regime}/fused={fuse}")
         outs.append(got)
     worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
@@ -220,6 +220,37 @@ def test_replay_with_the_projection_that_stores_into_the_pages(cuda_device, plai
             att.FUSE_QKV, att.FUSE_QKV_FILL = before
         assert ("gemm_bf16_cluster_qkv" in seen.names) == fuse
         _compare(got, ref, dtype, f"{which}/{regime}/fused={fuse}")
+        outs.append(got)
+    worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
+    assert worst <= TOL[dtype], f"fused and separate kernels differ by {worst:.3g}"
+
+
+@pytest.mark.parametrize("which", ["F", "O", "M"])
+def test_replay_with_the_activation_in_the_projection(cuda_device, plain_logits, which):
+    """Steps of few tokens run the gate/up projection with the activation in its epilogue.
+    Same logits as the plain implementation, and (to bfloat16 rounding) as the same steps
+    with the product and the activation as two kernels."""
+    from binfer_b200.csrc import ops
+    import importlib
+    mlp = importlib.import_module("binfer_b200.parts.mlp")
+    dtype = torch.bfloat16
+    reqs = _requests(which, (55, 61))
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    steps = H.trace_mixed(reqs)
+    ps = H.TINY[which]["page_size"]
+    outs = []
+    before = mlp.FUSE_SWIGLU
+    for fuse in (True, False):
+        mlp.FUSE_SWIGLU = fuse
+        seen = _Names()
+        ops.set_profiler(seen)
+        try:
+            got = H.run_trace(_runner(model_dir, dtype, ps, H.peak_pages(steps, ps)), steps)
+        finally:
+            ops.set_profiler(None)
+            mlp.FUSE_SWIGLU = before
+        assert ("gemm_bf16_swiglu" in seen.names) == fuse
+        _compare(got, ref, dtype, f"{which}/mixed/swiglu={fuse}")
         outs.append(got)
     worst = max(H.rel_err(outs[0][k], outs[1][k]) for k in outs[0])
     assert worst <= TOL[dtype], f"fused and separate kernels differ by {worst:.3g}"
