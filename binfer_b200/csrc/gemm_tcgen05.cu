@@ -38,6 +38,8 @@
 #include "common.cuh"
 #include "tma_utils.cuh"
 
+#include <stdlib.h>
+
 #include "umma_utils.cuh"
 
 namespace {
@@ -47,6 +49,7 @@ struct GemmParams {
   int tiles_t, tiles_f;        // tiles over tokens (128 each) and over features (bn each)
   int bn;                      // feature rows per tile, multiple of 16
   int a_rows;                  // token rows fetched per tile, multiple of 8
+  int mma_rows;                // M of the tcgen05.mma: 128, or 64 with at most 16 tokens
   int stages;
   long long ldo;               // row stride of the output, in elements
   int* err;
@@ -131,7 +134,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     if (lane == 0) {
       // c = float, a = b = bf16, both K-major, N = bn, M = 128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
-                             ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(p.mma_rows >> 4) << 24);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int u = blockIdx.x; u < units && !*abort; u += gridDim.x) {
@@ -331,6 +334,12 @@ BF_EXPORT int bf_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
   p.tiles_t = (tokens + BM - 1) / BM;
   p.tiles_f = (features + bn - 1) / bn;
   p.a_rows = tokens >= BM ? BM : ((tokens + 7) / 8) * 8;
+  // At most 16 tokens lie in tensor memory lanes 0..15 whether the product has 128 rows or
+  // 64; 64 rows are half the tensor work per weight byte (a decode step runs at the board's
+  // power limit, so that is clock: see gemm_tcgen05_cluster.cu).
+  static const int rows =
+      getenv("BINFER_B200_GEMM_MMA_ROWS") ? atoi(getenv("BINFER_B200_GEMM_MMA_ROWS")) : 64;
+  p.mma_rows = rows == 64 && tokens <= 16 ? 64 : 128;
   p.stages = 0;
   p.err = err;
   return out_dtype == BF_DTYPE_F32

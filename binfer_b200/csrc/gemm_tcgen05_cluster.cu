@@ -44,6 +44,7 @@ struct ClusterGemmParams {
   int cluster;                  // CTAs per tile
   int stages;
   int issuers;                  // threads that issue tcgen05.mma, 1 or 2
+  int mma_rows;                 // M of the tcgen05.mma: 128, or 64 (at most 16 token rows)
   int tok_rows;                 // token rows fetched and reduced: 16, 32 or 64 (>= tokens)
   int tmem_cols;                // tensor memory columns the CTA allocates (a power of two)
   int acc_stride;               // columns between the two issuers' accumulators
@@ -139,9 +140,10 @@ __device__ __forceinline__ void rotate_pairs(float (&v)[8], const QkvToken& k) {
 // One stage's weight rows: the tile's bn rows, or (SwiGLU form) bn/2 gate rows and the bn/2
 // up rows of the same outputs, one behind the other (bn/2 is a multiple of 8, so the second
 // box starts on a swizzle period).
+template <bool SWIGLU>
 __device__ __forceinline__ void load_weights(const ClusterGemmParams& p, const CUtensorMap* map_w,
                                              uint8_t* dst, uint64_t* bar, int k, int tile) {
-  if (!p.act_out) {
+  if (!SWIGLU) {
     tma_load_2d(dst, map_w, bar, k, tile * p.bn);
   } else {
     const int h = p.bn / 2;
@@ -151,12 +153,17 @@ __device__ __forceinline__ void load_weights(const ClusterGemmParams& p, const C
 }
 __device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
 
-template <typename OutT>
+// The epilogue's form is a template parameter, so that each instance carries only its own
+// code: with all four behind run-time tests the plain product was 3 % slower.
+enum { FORM_PLAIN = 0, FORM_ADD_NORM = 1, FORM_QKV = 2, FORM_SWIGLU = 3 };
+
+template <typename OutT, int FORM>
 __global__ void __launch_bounds__(192, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                     const ClusterGemmParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  constexpr bool kNorm = FORM == FORM_ADD_NORM, kQkv = FORM == FORM_QKV, kAct = FORM == FORM_SWIGLU;
   BF_TRACE_POINT(10 * BF_TR_GEMM);
   bf_pdl_trigger();
   uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -169,8 +176,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   float* recv = reinterpret_cast<float*>(base + CL_BAR_BYTES);
   const int slice = p.bn / p.cluster;                          // columns owned per CTA
   const int own_tokens = (p.tokens + p.cluster - 1) / p.cluster;   // (q/k/v form) per CTA
-  const int recv_bytes = p.act_out ? 0
-                         : p.q_out ? p.cluster * own_tokens * p.bn * 4
+  const int recv_bytes = kAct ? 0
+                         : kQkv ? p.cluster * own_tokens * p.bn * 4
                                    : p.cluster * p.tok_rows * slice * 4;
   uint8_t* tiles = base + CL_BAR_BYTES + ((recv_bytes + 1023) & ~1023);
 
@@ -213,7 +220,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   if (warp == 2 && lane == 0) {
     for (int i = 0; i < pre; ++i) {
       mbar_expect_tx(full + i, stage_bytes);
-      load_weights(p, &map_w, tiles + (size_t)i * stage_bytes + a_bytes, full + i, (kc0 + i) * BK,
+      load_weights<kAct>(p, &map_w, tiles + (size_t)i * stage_bytes + a_bytes, full + i, (kc0 + i) * BK,
                    tile);
     }
   }
@@ -231,7 +238,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         uint8_t* dst = tiles + (size_t)stage * stage_bytes;
         mbar_expect_tx(full + stage, stage_bytes);
         tma_load_2d(dst, &map_x, full + stage, kc * BK, 0);
-        load_weights(p, &map_w, dst + a_bytes, full + stage, kc * BK, tile);
+        load_weights<kAct>(p, &map_w, dst + a_bytes, full + stage, kc * BK, tile);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
@@ -245,7 +252,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     const int who = warp == 1 ? 0 : 1;
     if (lane == 0 && who < p.issuers && kc1 - kc0 > who) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
-                             ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(p.mma_rows >> 4) << 24);
       const uint32_t acc = tmem_base + (uint32_t)(who * p.acc_stride);
       bool ok = true;
       for (int n = who; n < kc1 - kc0; n += p.issuers) {
@@ -271,12 +278,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     // than 32 token rows) reads lanes 32..63.  A lane holds one token's row of the partial sum.
     const int row = (warp == 5 ? 32 : 0) + lane;
     const uint32_t lanes = (uint32_t)(warp == 5 ? 32 : 0) << 16;
-    const int width = p.act_out ? p.bn / 2 : p.bn;          // columns to walk: outputs or sums
+    const int width = kAct ? p.bn / 2 : p.bn;          // columns to walk: outputs or sums
     const int chunks = (width + 15) / 16, half = (chunks + 1) / 2;
     const int c_begin = warp == 4 ? half * 16 : 0, c_end = warp == 0 ? half * 16 : chunks * 16;
     // (SwiGLU form) the factor of this lane's row, worked out while the products run
     float factor = 1.f;
-    if (p.act_out && p.rs.partials)
+    if (kAct && p.rs.partials)
       for (int t = (warp == 5 ? 32 : 0); t < p.tokens && t < (warp == 5 ? 64 : 32); ++t) {
         const float ft = bf_row_factor(p.rs, t, lane);
         if (t == row) factor = ft;
@@ -287,7 +294,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     tc_fence_after();
     BF_TRACE_POINT(10 * BF_TR_GEMM + 5);
     const uint32_t my_recv = smem_u32(recv);
-    for (int c0 = c_begin; c0 < c_end && p.act_out; c0 += 16) {
+    for (int c0 = c_begin; c0 < c_end && kAct; c0 += 16) {
       // gate columns c0.., up columns bn/2 + c0.. of both issuers' accumulators
       const int h = p.bn / 2;
       uint32_t g[16], u[16];
@@ -332,7 +339,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       }
     }
-    for (int c0 = c_begin; c0 < c_end && !p.act_out; c0 += 16) {
+    for (int c0 = c_begin; c0 < c_end && !kAct; c0 += 16) {
       uint32_t r[16];
       if (have) {
         if (p.issuers == 2 && kc1 - kc0 >= 2) {          // with the second issuer's share
@@ -349,7 +356,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
         for (int j = 0; j < 16; ++j) r[j] = 0u;     // no K steps here (or a timeout): send zeros
       }
-      if (p.q_out) {
+      if (kQkv) {
         // the token's owner gets its whole row: recv[rank][own token][column]
         if (row < p.tokens) {
           const int at = (rank * own_tokens + row / p.cluster) * p.bn + c0;
@@ -382,9 +389,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // The fused epilogue's inputs do not depend on the product: those of a thread's first item
   // are asked for before the cluster waits for its slowest member (further items' later).
   const int groups = slice / 4;
-  const int n_plain = p.q_out || p.act_out ? 0 : p.tokens * groups;
+  const int n_plain = kQkv || kAct ? 0 : p.tokens * groups;
   float pre_r[4] = {0.f, 0.f, 0.f, 0.f}, pre_w[4] = {0.f, 0.f, 0.f, 0.f};
-  if (p.resid && (int)threadIdx.x < n_plain) {
+  if (kNorm && (int)threadIdx.x < n_plain) {
     const int g = threadIdx.x / p.tokens, t = threadIdx.x - g * p.tokens;
     const int f = tile * p.bn + rank * slice + g * 4;
 #pragma unroll
@@ -400,18 +407,18 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // asked for before the cluster's barrier.  The warps take their turns in the order in which
   // they are free: 2 has issued its loads long before the sums are there, 5 idles unless there
   // are more than 32 token rows, 1 and 3 issue products to the end, 4 and 0 send.
-  const int heads_per_tile = p.q_out ? p.bn / p.d : 0;
-  const int n_mine = p.q_out && p.tokens > rank ? (p.tokens - rank + p.cluster - 1) / p.cluster : 0;
+  const int heads_per_tile = kQkv ? p.bn / p.d : 1;
+  const int n_mine = kQkv && p.tokens > rank ? (p.tokens - rank + p.cluster - 1) / p.cluster : 0;
   const int turn = warp == 2 ? 0 : warp == 5 ? 1 : warp == 1 ? 2 : warp == 3 ? 3 : warp == 4 ? 4 : 5;
   QkvToken tk;
-  if (turn < n_mine) tk = qkv_token(p, turn * p.cluster + rank, lane);
+  if (kQkv && turn < n_mine) tk = qkv_token(p, turn * p.cluster + rank, lane);
 
   // every thread of every CTA of the cluster: partials are in place after this
   BF_TRACE_POINT(10 * BF_TR_GEMM + 3);
   cluster_sync_all();
   BF_TRACE_POINT(10 * BF_TR_GEMM + 4);
 
-  for (int it = turn * heads_per_tile; it < n_mine * heads_per_tile; ++it) {
+  for (int it = turn * heads_per_tile; kQkv && it < n_mine * heads_per_tile; ++it) {
     const int lt = it / heads_per_tile, hh = it - lt * heads_per_tile;
     if (hh == heads_per_tile - 1) it += 5 * heads_per_tile;      // on to the token 6 further
     const int t = lt * p.cluster + rank;
@@ -479,7 +486,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       sum[3] += v.w;
     }
     const int f = tile * p.bn + rank * slice + g * 4;
-    if (!p.resid) {
+    if (!kNorm) {
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         if (f + k < p.features) bf_st(out + (size_t)t * p.ldo + f + k, sum[k]);
@@ -503,7 +510,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
           make_float4(sq[0], sq[1], sq[2], sq[3]);
     }
   }
-  if (p.resid) {
+  if (kNorm) {
     // one partial sum of squares per token and CTA, its columns added in ascending order
     __syncthreads();
     for (int t = threadIdx.x; t < p.tokens; t += blockDim.x) {
@@ -526,7 +533,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // happened before the cluster barrier above, so nothing more is needed here
 }
 
-template <typename OutT>
+template <typename OutT, int FORM>
 int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p, long long ldx,
                    long long ldw, cudaStream_t stream) {
   CUtensorMap mx, mw;
@@ -550,6 +557,13 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   p.stages = stages;
   static const int issuers = getenv("BINFER_B200_GEMM_ISSUERS") ? atoi(getenv("BINFER_B200_GEMM_ISSUERS")) : 2;
   p.issuers = issuers == 1 ? 1 : 2;
+  // With at most 16 token rows (rows 0..15 lie in tensor memory lanes 0..15 for both shapes)
+  // a 64-row product does: half the tensor work per weight byte.  The time of one product is
+  // the same, but a decode step is long enough to run into the board's power limit, and with
+  // 128-row products for 8 tokens the SM clock settled near 1750 MHz instead of 1965 (36
+  // layers, batch 8: 4.28 against 4.12 ms a step with every projection on this kernel).
+  static const int rows = getenv("BINFER_B200_GEMM_MMA_ROWS") ? atoi(getenv("BINFER_B200_GEMM_MMA_ROWS")) : 64;
+  p.mma_rows = rows == 64 && p.tok_rows <= 16 ? 64 : 128;
   int need = p.issuers * p.bn, cols = 32;
   while (cols < need) cols *= 2;
   p.tmem_cols = cols;
@@ -560,7 +574,7 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   // (Seen once, with the shared memory capped at 110 KB for an experiment: the launch failed.)
   size_t smem = fixed + (size_t)stages * stage_bytes;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  auto kern = gemm_cluster_kernel<OutT>;
+  auto kern = gemm_cluster_kernel<OutT, FORM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -652,8 +666,9 @@ BF_EXPORT int bf_gemm_bf16_cluster(const void* x, const void* w, void* out, int 
   p.partials = nullptr;
   p.ldr = p.ldxt = 0;
   return out_dtype == BF_DTYPE_F32
-             ? launch_cluster<float>(x, w, (float*)out, p, ldx, ldw, stream)
-             : launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)out, p, ldx, ldw, stream);
+             ? launch_cluster<float, FORM_PLAIN>(x, w, (float*)out, p, ldx, ldw, stream)
+             : launch_cluster<__nv_bfloat16, FORM_PLAIN>(x, w, (__nv_bfloat16*)out, p, ldx, ldw,
+                                                         stream);
 }
 
 // The same product with the residual stream and the next norm in its epilogue:
@@ -691,7 +706,8 @@ BF_EXPORT int bf_gemm_bf16_cluster_add_norm(const void* x, const void* w, int to
   p.ldr = ldr;
   p.ldxt = ldxt;
   if (n_partials) *n_partials = ((features + bn - 1) / bn) * cluster;
-  return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
+  return launch_cluster<__nv_bfloat16, FORM_ADD_NORM>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw,
+                                                     stream);
 }
 
 // How many clusters of c CTAs of this kernel can be resident at once (0 on an error).
@@ -699,7 +715,7 @@ static int resident_clusters(int c) {
   static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
   if (c < 1 || c > 8) return 0;
   if (known[c] >= 0) return known[c];
-  auto kern = gemm_cluster_kernel<__nv_bfloat16>;
+  auto kern = gemm_cluster_kernel<__nv_bfloat16, FORM_QKV>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
       cudaSuccess) {
     cudaGetLastError();
@@ -808,7 +824,8 @@ BF_EXPORT int bf_gemm_bf16_cluster_qkv(
   p.rs.count = row_count;
   p.rs.inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
   p.rs.eps = row_eps;
-  return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
+  return launch_cluster<__nv_bfloat16, FORM_QKV>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw,
+                                                     stream);
 }
 
 // Tile for the SwiGLU form: the narrowest tile (bn = 2 h weight rows for h outputs, h a multiple
@@ -851,7 +868,8 @@ BF_EXPORT int bf_gemm_bf16_swiglu(const void* x, const void* w, int tokens, int 
   p.rs.count = row_count;
   p.rs.inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
   p.rs.eps = row_eps;
-  return launch_cluster<__nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw, stream);
+  return launch_cluster<__nv_bfloat16, FORM_SWIGLU>(x, w, (__nv_bfloat16*)nullptr, p, ldx, ldw,
+                                                     stream);
 }
 
 BF_TRACE_READER(bf_trace_read_gemm_tcgen05_cluster)

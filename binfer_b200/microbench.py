@@ -233,7 +233,8 @@ def step_timeline(a):
     t0 = prev = events[0][0]
     print(f"# decode step, batch {B}, context {ctx}, {a.layers} layers; microseconds", flush=True)
     for t, c in events:
-        print(f"{(t - t0) / 1e3:10.2f} {(t - prev) / 1e3:8.2f}  {names.get(c // 10, '?'):18s} {phases[c % 10]}")
+        print(f"{(t - t0) / 1e3:10.2f} {(t - prev) / 1e3:8.2f}  {names.get(c // 10, '?'):18s} "
+              f"{phases[c % 10]}  [{c}]")
         prev = t
     print(json.dumps({"kernel": "step_timeline", "us": round((events[-1][0] - t0) / 1e3, 2),
                       "events": len(events), "batch": B, "ctx": ctx, "layers": a.layers}))
