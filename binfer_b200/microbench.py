@@ -162,6 +162,33 @@ def gemm(a):
            nbytes=(N * K + M * K + M * N) * 2, flops=2.0 * M * N * K, tokens=M, features=N, k=K)
 
 
+def swiglu(a):
+    """The gate/up projection with the activation in its epilogue (--tokens, --intermediate,
+    --k); --library times the library's product followed by the activation kernel."""
+    dev = torch.device("cuda:0")
+    M, I, K = a.tokens, a.intermediate, a.k
+    sets = max(2, int(3e8 // (2 * I * K * 2)) + 1)
+    ws = [(0.05 * torch.randn(2 * I, K, device=dev)).to(BF16) for _ in range(sets)]
+    x = torch.randn(M, K, device=dev).to(BF16)
+    out = torch.empty(M, I, device=dev, dtype=BF16)
+    gu = torch.empty(M, 2 * I, device=dev, dtype=BF16)
+    err = ops.error_word(dev)
+    if a.library:
+        name = "library product + silu_mul"
+
+        def two(w):
+            torch.mm(x, w.t(), out=gu)
+            ops.silu_mul(gu, out)
+        fns = [lambda w=w: two(w) for w in ws]
+    else:
+        bn = a.bn or ops.gemm_swiglu_plan(I, K, dev)
+        name = f"gemm_bf16_swiglu(bn={bn})"
+        fns = [lambda w=w: ops.gemm_bf16_swiglu(x, w, out, err, bn) for w in ws]
+    us = timed(fns, a.iters, a.warmup)
+    report(name, us, nbytes=(2 * I * K + M * K + M * I) * 2, flops=4.0 * M * I * K, tokens=M,
+           intermediate=I, k=K)
+
+
 def add_rmsnorm(a):
     dev = torch.device("cuda:0")
     T, H = a.tokens, a.hidden
@@ -244,7 +271,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m binfer_b200.microbench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["decode_attention", "prefill_attention", "gemm",
-                                       "add_rmsnorm", "step_timeline"])
+                                       "swiglu", "add_rmsnorm", "step_timeline"])
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
@@ -277,7 +304,8 @@ def main(argv=None):
     global GRAPH
     GRAPH = not a.no_graph
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention,
-     "gemm": gemm, "add_rmsnorm": add_rmsnorm, "step_timeline": step_timeline}[a.kernel](a)
+     "gemm": gemm, "swiglu": swiglu, "add_rmsnorm": add_rmsnorm,
+     "step_timeline": step_timeline}[a.kernel](a)
     return 0
 
 
