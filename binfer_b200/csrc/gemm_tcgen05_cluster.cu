@@ -21,6 +21,14 @@
 // result: one fixed order of summation, no atomics, no global workspace, and nothing spins
 // on another CTA (the cluster barrier is the hardware's).
 //
+// The product itself has 64 rows when there are at most 16 token rows (they lie in tensor
+// memory lanes 0..15 for both shapes), else 128.  What happens to the sums is the kernel's
+// FORM, a template parameter: stored as they are; added into the float residual stream with
+// the next RMSNorm prepared; (q/k/v projection) head norms, rotation and the store into the
+// cache pages, the tile's rows shared out by token instead of by column; (gate/up
+// projection, clusters of one CTA) the activation, from tensor memory straight to global
+// memory.  Each form is described at its export below.
+//
 // mbarrier waits are bounded (about a second); on a timeout the CTA sets BF_ERR_WAIT,
 // still contributes (zeros) and still joins the cluster barrier, frees TMEM and returns.
 // No TMA load uses multicast; every load reads this GPU's own memory.
