@@ -490,11 +490,11 @@ def gemm_bf16_cluster_qkv(x: torch.Tensor, w: torch.Tensor, q_w: Optional[torch.
 
 
 def gemm_swiglu_plan(inter: int, K: int, device: torch.device):
-    """bn for ``gemm_bf16_swiglu``, or None where its tiles would not fit one wave."""
+    """(bn, CTAs) for ``gemm_bf16_swiglu``, or None where its tiles would not fit one wave."""
     bn = _c_int(0)
     n = lib().bf_gemm_swiglu_plan(_c_int(inter), _c_int(K), _c_int(num_sms(device)),
                                   ctypes.byref(bn))
-    return bn.value if n > 0 else None
+    return (bn.value, n) if n > 0 else None
 
 
 def gemm_bf16_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,

@@ -181,7 +181,7 @@ def swiglu(a):
             ops.silu_mul(gu, out)
         fns = [lambda w=w: two(w) for w in ws]
     else:
-        bn = a.bn or ops.gemm_swiglu_plan(I, K, dev)
+        bn = a.bn or ops.gemm_swiglu_plan(I, K, dev)[0]
         name = f"gemm_bf16_swiglu(bn={bn})"
         fns = [lambda w=w: ops.gemm_bf16_swiglu(x, w, out, err, bn) for w in ws]
     us = timed(fns, a.iters, a.warmup)

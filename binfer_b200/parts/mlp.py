@@ -21,6 +21,8 @@ from .linear import cluster_token_limit, linear
 
 # BINFER_B200_FUSE_SWIGLU=0: the stacked gate/up projection and the activation as two kernels
 FUSE_SWIGLU = os.environ.get("BINFER_B200_FUSE_SWIGLU", "1") != "0"
+# ... and only where its tiles (at least 16 outputs each) give work to this share of the SMs
+FUSE_SWIGLU_FILL = 0.5
 
 
 class GatedMLP(FeedForward):
@@ -32,7 +34,7 @@ class GatedMLP(FeedForward):
         self.spec, self.hidden, self.prefix, self.env = spec, hidden_size, prefix, env
         self.inter = spec.intermediate_size
         self.w_gate_up = self.w_down = None
-        self._swiglu_bn = None
+        self._swiglu_plan = None
 
     def param_specs(self) -> List[ParamSpec]:
         p = self.prefix
@@ -68,12 +70,13 @@ class GatedMLP(FeedForward):
         if (not FUSE_SWIGLU or x.dtype != torch.bfloat16 or x.shape[0] > cluster_token_limit()
                 or self.inter % 8):
             return False
-        if self._swiglu_bn is None:
-            self._swiglu_bn = ops.gemm_swiglu_plan(self.inter, x.shape[1], x.device) or 0
-        if not self._swiglu_bn:
+        if self._swiglu_plan is None:
+            self._swiglu_plan = ops.gemm_swiglu_plan(self.inter, x.shape[1], x.device) or False
+        plan = self._swiglu_plan
+        if not plan or plan[1] < FUSE_SWIGLU_FILL * ops.num_sms(x.device):
             return False
-        return ops.gemm_bf16_swiglu(x, self.w_gate_up, h, ops.error_word(x.device),
-                                    self._swiglu_bn, row_scale=row_scale)
+        return ops.gemm_bf16_swiglu(x, self.w_gate_up, h, ops.error_word(x.device), plan[0],
+                                    row_scale=row_scale)
 
 
 register_ffn("gated_mlp", GatedMLP)

@@ -420,8 +420,8 @@ def test_gemm_swiglu_matches_product_then_activation(cuda_device, T, I, K, bn, s
         scale = ops.RowScale((torch.rand(T, 130, generator=g) * 8).to(dev), 512, 1e-6)
         f = scale.factors().double().cpu()
     if bn == 0:
-        bn = ops.gemm_swiglu_plan(I, K, dev)
-        assert bn and bn % 16 == 0 and -(-I // (bn // 2)) <= ops.num_sms(dev)
+        bn, ctas = ops.gemm_swiglu_plan(I, K, dev)
+        assert bn % 16 == 0 and ctas == -(-I // (bn // 2)) <= ops.num_sms(dev)
     out = torch.full((T, I), 7.0, device=dev, dtype=BF16)
     err = _err(dev)
     assert ops.gemm_bf16_swiglu(x, w, out, err, bn, row_scale=scale)

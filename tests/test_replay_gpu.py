@@ -239,16 +239,16 @@ def test_replay_with_the_activation_in_the_projection(cuda_device, plain_logits,
     steps = H.trace_mixed(reqs)
     ps = H.TINY[which]["page_size"]
     outs = []
-    before = mlp.FUSE_SWIGLU
+    before = mlp.FUSE_SWIGLU, mlp.FUSE_SWIGLU_FILL
     for fuse in (True, False):
-        mlp.FUSE_SWIGLU = fuse
+        mlp.FUSE_SWIGLU, mlp.FUSE_SWIGLU_FILL = fuse, 0.0     # (also where few SMs get a tile)
         seen = _Names()
         ops.set_profiler(seen)
         try:
             got = H.run_trace(_runner(model_dir, dtype, ps, H.peak_pages(steps, ps)), steps)
         finally:
             ops.set_profiler(None)
-            mlp.FUSE_SWIGLU = before
+            mlp.FUSE_SWIGLU, mlp.FUSE_SWIGLU_FILL = before
         assert ("gemm_bf16_swiglu" in seen.names) == fuse
         _compare(got, ref, dtype, f"{which}/mixed/swiglu={fuse}")
         outs.append(got)
