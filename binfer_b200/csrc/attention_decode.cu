@@ -20,6 +20,8 @@
 // Scratch: part_o float [rows, nh, max_splits, D], part_ml float [rows, nh, max_splits, 2].
 #include <float.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -227,94 +229,117 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ q,
   }
 }
 
-// Merge the splits of each (row, head) in ascending order and normalise.  One block of 128
-// threads per (row, head).  The kernel is all latency (a few KB from L2 per block), so it is
-// built around the number of dependent round trips: the row's position and, speculatively,
-// each thread's split's (m, l) pair are asked for together; the weights exp2(m_s - M) go to
-// shared memory; then every thread asks for the partial outputs of its column for 32 splits
-// at once.  Sums run in one fixed order (ascending splits per thread, then threads).  Its
-// shared memory is kept to half a KB so that its blocks fit beside the attention kernel's,
-// which leave little: the blocks are then resident (and have triggered their dependents)
-// before the attention ends.
-#define MERGE_PASS 128
-template <int D>
+// Merge the splits of each (row, head) and normalise.  The kernel is all latency (a few KB
+// from L2 per (row, head); 128 KB at 32 768 keys), so it is built around the number of
+// dependent round trips and needs neither shared memory nor a block-wide barrier: a warp owns
+// 16 (or 32) columns of one (row, head) for all of its splits.  Lane = (4 columns, one of 8 (or
+// 4) classes of splits): the lane's splits are those with index = class mod 8.  First pass: every (m, l)
+// pair of the lane's splits, up to 32 in flight at once (asked for, when there is no window,
+// together with the row's position, whose value says which of them count), gives the
+// maximum M over the classes by shuffles.  Second pass, 16 splits a lane at once: the pairs
+// again (from L2) with the partial outputs, weights exp2(m - M), sums over the lane's splits
+// in ascending order, then over the classes in one fixed tree.  32 splits (4096 keys) take
+// two round trips, 256 splits three; the kernel before this one (a block per (row, head),
+// a thread per column, 32 splits at once) took two and ten.
+// Two shapes of it.  4 classes and 8 / 8 in flight (a block per (row, head), 40 registers)
+// is the one for most steps.  8 classes and 32 / 16 in flight (two blocks per (row, head), 86
+// registers) is launched where the rows' contexts may reach 16 384 keys (128 splits) and
+// there are at most 1 024 (row, head) pairs: 29.8 against 39.5 us for one row of 32 768 keys,
+// but 28.0 against 26.3 us for 8 rows of 4 096 and 188 against 177 us for 64 rows, where fewer
+// of its blocks are resident beside the attention kernel's and they come in more waves.
+// (row, head) pairs up to which the first shape is launched (BINFER_B200_MERGE_FEW_PAIRS)
+static int merge_few_pairs() {
+  static const int n = getenv("BINFER_B200_MERGE_FEW_PAIRS") ? atoi(getenv("BINFER_B200_MERGE_FEW_PAIRS")) : 1024;
+  return n;
+}
+#define MERGE_FEW_PAIRS merge_few_pairs()
+#define MERGE_MANY_SPLITS 128
+template <int D, int MERGE_CLASSES, int UA, int UB>
 __global__ void __launch_bounds__(128)
 decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                               const int* __restrict__ rows, const int* __restrict__ positions,
                               __nv_bfloat16* __restrict__ out, int nh, int window,
                               int max_splits) {
-  __shared__ float wgt[MERGE_PASS];
-  __shared__ float red[4];
   BF_TRACE_POINT(10 * BF_TR_MERGE);
   bf_pdl_trigger();
   bf_pdl_wait();
   BF_TRACE_POINT(10 * BF_TR_MERGE + 1);
   const int r = blockIdx.x, h = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int CG = 32 / MERGE_CLASSES;                   // groups of 4 columns a warp covers
+  const int cb = (blockIdx.z * 4 + warp) * CG * 4;         // the warp's first column
+  if (cb >= D) return;
+  const int cg = lane % CG, sc = lane / CG;                // column group of 4, class of splits
   const size_t base = ((size_t)r * nh + h) * max_splits;
   const float2* ml2 = reinterpret_cast<const float2*>(part_ml) + base;
   const int t = rows ? rows[r] : r;
-  const float2 ml0 = tid < max_splits ? __ldcg(ml2 + tid) : make_float2(-INFINITY, 0.f);
+  const float2 none = make_float2(-INFINITY, 0.f);
+
+  // first pass, first chunk: asked for before the position is known where the first split is 0
+  float2 first[UA];
+  if (window <= 0) {
+#pragma unroll
+    for (int u = 0; u < UA; ++u) {
+      const int i = sc + MERGE_CLASSES * u;
+      first[u] = i < max_splits ? __ldcg(ml2 + i) : none;
+    }
+  }
   const int p = positions[t];
   const int j0 = window > 0 ? max(0, p - window + 1) : 0;
-  const int s_first = j0 / DEC_SPLIT, s_last = p / DEC_SPLIT;
-  // thread tid owns the splits tid, tid + 128, ...; the first came with the position
-  float m_loc = -INFINITY;
-  for (int s = tid; s <= s_last; s += 128)
-    if (s >= s_first) m_loc = fmaxf(m_loc, (s == tid ? ml0 : __ldcg(ml2 + s)).x);
-  m_loc = warp_max(m_loc);
-  if (lane == 0) red[warp] = m_loc;
-  __syncthreads();
-  const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  __syncthreads();
-  float l_loc = 0.f;
-  for (int s = tid; s <= s_last; s += 128)
-    if (s >= s_first) {
-      const float2 ml = s == tid ? ml0 : __ldcg(ml2 + s);
-      const float w = exp2f(ml.x - M);
-      if (s - s_first < MERGE_PASS) wgt[s - s_first] = w;
-      l_loc += ml.y * w;
+  const int s_first = j0 / DEC_SPLIT, n = p / DEC_SPLIT - s_first + 1;
+  const float2* ml = ml2 + s_first;
+  float M = -INFINITY;
+  for (int k0 = 0; k0 < n; k0 += MERGE_CLASSES * UA) {
+    float2 v[UA];
+#pragma unroll
+    for (int u = 0; u < UA; ++u) {
+      const int i = k0 + sc + MERGE_CLASSES * u;
+      v[u] = i >= n ? none : (k0 == 0 && window <= 0) ? first[u] : __ldcg(ml + i);
     }
-  l_loc = warp_sum(l_loc);
-  if (lane == 0) red[warp] = l_loc;
-  __syncthreads();                                       // also: the weights are in place
-  const float inv = 1.f / (((red[0] + red[1]) + red[2]) + red[3]);
+#pragma unroll
+    for (int u = 0; u < UA; ++u) M = fmaxf(M, v[u].x);
+  }
+#pragma unroll
+  for (int d = CG; d <= 16; d *= 2) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
 
-  constexpr int COLS = (D + 127) / 128;
-  float acc[COLS];
+  float L = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* po = part_o + (base + s_first) * D + cb + cg * 4;
+  for (int k0 = 0; k0 < n; k0 += MERGE_CLASSES * UB) {
+    float2 v[UB];
+    float4 o[UB];
 #pragma unroll
-  for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
-  const int n = s_last - s_first + 1;
-  for (int p0 = 0; p0 < n; p0 += MERGE_PASS) {
-    const int np = min(MERGE_PASS, n - p0);
-    if (p0 > 0) {                                        // contexts of more than 16384 keys
-      __syncthreads();
-      for (int i = tid; i < np; i += 128) wgt[i] = exp2f(__ldcg(ml2 + s_first + p0 + i).x - M);
-      __syncthreads();
+    for (int u = 0; u < UB; ++u) {
+      const int i = k0 + sc + MERGE_CLASSES * u;
+      v[u] = i < n ? __ldcg(ml + i) : none;
+      o[u] = i < n ? __ldcg(reinterpret_cast<const float4*>(po + (size_t)i * D))
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int i = 0; i < COLS; ++i) {
-      const int c = tid + i * 128;
-      if (c < D) {
-        const float* po = part_o + (base + s_first + p0) * D + c;
-        float a = acc[i];
-        for (int c0 = 0; c0 < np; c0 += 32) {
-          float v[32];
-#pragma unroll
-          for (int u = 0; u < 32; ++u)
-            v[u] = c0 + u < np ? __ldcg(po + (size_t)(c0 + u) * D) : 0.f;
-#pragma unroll
-          for (int u = 0; u < 32; ++u)
-            if (c0 + u < np) a += v[u] * wgt[c0 + u];
-        }
-        acc[i] = a;
-      }
+    for (int u = 0; u < UB; ++u) {
+      const float w = v[u].x == -INFINITY ? 0.f : exp2f(v[u].x - M);
+      L += v[u].y * w;
+      acc.x += o[u].x * w;
+      acc.y += o[u].y * w;
+      acc.z += o[u].z * w;
+      acc.w += o[u].w * w;
     }
   }
 #pragma unroll
-  for (int i = 0; i < COLS; ++i) {
-    const int c = tid + i * 128;
-    if (c < D) out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(acc[i] * inv);
+  for (int d = CG; d <= 16; d *= 2) {                       // over the classes: one fixed tree
+    L += __shfl_xor_sync(0xffffffffu, L, d);
+    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, d);
+    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, d);
+    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, d);
+    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, d);
+  }
+  if (sc == 0) {
+    const float inv = 1.f / L;
+    uint2 packed;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+    o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    o2[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + ((size_t)t * nh + h) * D + cb + cg * 4) = packed;
   }
 }
 
@@ -344,7 +369,11 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
       num_pages, window, max_splits, scale * 1.4426950408889634f, err);
   int e = bf_launch_status();
   if (e) return e;
-  decode_attention_merge_kernel<D><<<dim3(n_rows, nh), 128, 0, stream>>>(
+  if (n_rows * nh <= MERGE_FEW_PAIRS && max_splits >= MERGE_MANY_SPLITS)
+    decode_attention_merge_kernel<D, 8, 32, 16><<<dim3(n_rows, nh, (D + 63) / 64), 128, 0, stream>>>(
+      part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);
+  else
+    decode_attention_merge_kernel<D, 4, 8, 8><<<dim3(n_rows, nh, (D + 127) / 128), 128, 0, stream>>>(
       part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh, window, max_splits);
   return bf_launch_status();
 }
@@ -383,11 +412,17 @@ BF_EXPORT int bf_decode_attention_merge(const float* part_o, const float* part_m
                                         const int* positions, void* out, int n_rows, int nh, int d,
                                         int window, int max_splits, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-#define BF_MERGE_CASE(DD)                                                                  \
-  case DD:                                                                                 \
-    return bf_launch_pdl(decode_attention_merge_kernel<DD>, dim3(n_rows, nh), dim3(128), 0,  \
-                         stream, part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh,  \
-                         window, max_splits)
+#define BF_MERGE_CASE(DD)                                                                     \
+  case DD:                                                                                    \
+    return n_rows * nh <= MERGE_FEW_PAIRS && max_splits >= MERGE_MANY_SPLITS                  \
+               ? bf_launch_pdl(decode_attention_merge_kernel<DD, 8, 32, 16>,                  \
+                               dim3(n_rows, nh, (DD + 63) / 64), dim3(128), 0, stream, part_o, \
+                               part_ml, rows, positions, (__nv_bfloat16*)out, nh, window,     \
+                               max_splits)                                                    \
+               : bf_launch_pdl(decode_attention_merge_kernel<DD, 4, 8, 8>,                    \
+                               dim3(n_rows, nh, (DD + 127) / 128), dim3(128), 0, stream,      \
+                               part_o, part_ml, rows, positions, (__nv_bfloat16*)out, nh,     \
+                               window, max_splits)
   switch (d) {
     BF_MERGE_CASE(32);
     BF_MERGE_CASE(64);
