@@ -267,18 +267,20 @@ def test_decode_attention_persistent_ring_wraps(cuda_device, nh, nkv, d, ps, win
     assert torch.equal(out, again), "the result depends on timing"
 
 
+@pytest.mark.parametrize("window", [None, 5000])
 @pytest.mark.parametrize("variant", ["cp_async", "tma", "persistent"])
-def test_decode_attention_more_splits_than_one_merge_pass(cuda_device, variant):
-    """Contexts beyond 16384 keys: more 128-key splits than the merge keeps weights for at
-    once.  One key far back is made to stand out, so a lost pass would show."""
+def test_decode_attention_more_splits_than_one_merge_pass(cuda_device, variant, window):
+    """Contexts beyond 16384 keys: the merge kernel's shape for many splits, more of them than
+    a lane asks for at once, and (with a window) a first split that is not split 0.  One key
+    far back is made to stand out, so a lost pass would show."""
     from binfer_b200.csrc import ops
     nh, nkv, d, ps = 4, 2, 64, 64
     ctxs, qlens = [20000, 16385, 300], [1, 1, 1]
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
-                                                   qlens, None, True, seed=5)
+                                                   qlens, window, True, seed=5)
     out = torch.zeros_like(q)
     err = _err(cuda_device)
-    ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, None,
+    ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, window,
                          d ** -0.5, max(ctxs), err, variant=variant)
     assert int(err.item()) == 0
     _close(out, ref, BF16)
