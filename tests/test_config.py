@@ -95,3 +95,50 @@ def test_memory_arithmetic():
         vocab_size=151936))
     assert c.kv_bytes_per_token(2) == 147456
     assert abs(c.num_parameters() - 8.19e9) < 0.01e9
+
+
+def test_position_encoding_with_tensors_of_its_own_is_part_of_the_checkpoint():
+    """A position encoding is chosen by its spec's kind like every part; one that names
+    tensors adds them, under the mixer's prefix, to what a checkpoint must hold; an unknown
+    kind is refused with the list of known ones.  (No GPU: only the list of tensors.)"""
+    from dataclasses import dataclass
+
+    from binfer_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NameLayout,
+                                    NormSpec, RopeSpec, ScheduleEntry)
+    from binfer_b200.parts import PositionEncoding, param_specs_for, register_position
+    from binfer_b200.weights import ParamSpec
+
+    @dataclass(frozen=True)
+    class TableSpec:
+        kind: str = "test_cpu_position_table"
+        entries: int = 5
+
+    class Table(PositionEncoding):
+        def __init__(self, spec, head_dim, env):
+            self.spec, self.head_dim = spec, head_dim
+
+        def param_specs(self, prefix):
+            return [ParamSpec(prefix + "position_table.weight", (self.spec.entries, self.head_dim))]
+
+    register_position("test_cpu_position_table", Table)
+    norm = NormSpec(eps=1e-6)
+
+    def model(position):
+        attn = AttentionSpec(num_heads=2, num_kv_heads=1, head_dim=16, position=position)
+        layers = (LayerSpec(mixer=attn, ffn=GatedMLPSpec(intermediate_size=24), norm=norm),)
+        return ModelSpec(architecture="ToyForCausalLM", hidden_size=32, vocab_size=11, layers=layers,
+                         schedule=(ScheduleEntry(0),), final_norm=norm, tie_word_embeddings=True,
+                         names=NameLayout())
+
+    specs = {s.name: s.shape for s in param_specs_for(model(TableSpec()))}
+    assert specs["model.layers.0.self_attn.position_table.weight"] == (5, 16)
+    plain = {s.name for s in param_specs_for(model(RopeSpec(theta=1e4)))}
+    assert not any("position_table" in n for n in plain)
+    assert set(specs) - plain == {"model.layers.0.self_attn.position_table.weight"}
+
+    @dataclass(frozen=True)
+    class Unknown:
+        kind: str = "test_no_such_position"
+
+    with pytest.raises(KeyError, match="position encoding.*test_no_such_position"):
+        param_specs_for(model(Unknown()))
