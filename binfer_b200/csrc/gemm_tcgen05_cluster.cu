@@ -21,9 +21,8 @@
 // result: one fixed order of summation, no atomics, no global workspace, and nothing spins
 // on another CTA (the cluster barrier is the hardware's).
 //
-// The product itself has 64 rows when there are at most 16 token rows (they lie in tensor
-// memory lanes 0..15 for both shapes), else 128.  What happens to the sums is the kernel's
-// FORM, a template parameter: stored as they are; added into the float residual stream with
+// The product itself has 64 rows when there are at most 32 token rows, else 128.  What
+// happens to the sums is the kernel's FORM, a template parameter: stored as they are; added into the float residual stream with
 // the next RMSNorm prepared; (q/k/v projection) head norms, rotation and the store into the
 // cache pages, the tile's rows shared out by token instead of by column; (gate/up
 // projection, clusters of one CTA) the activation, from tensor memory straight to global
@@ -52,7 +51,7 @@ struct ClusterGemmParams {
   int cluster;                  // CTAs per tile
   int stages;
   int issuers;                  // threads that issue tcgen05.mma, 1 or 2
-  int mma_rows;                 // M of the tcgen05.mma: 128, or 64 (at most 16 token rows)
+  int mma_rows;                 // M of the tcgen05.mma: 128, or 64 (at most 32 token rows)
   int tok_rows;                 // token rows fetched and reduced: 16, 32 or 64 (>= tokens)
   int tmem_cols;                // tensor memory columns the CTA allocates (a power of two)
   int acc_stride;               // columns between the two issuers' accumulators
@@ -281,10 +280,14 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       }
       if (ok) umma_commit(acc_full);
     }
-  } else if (warp == 0 || warp == 4 || (warp == 5 && p.tok_rows > 32)) {
-    // Warps 0 and 4 may both read TMEM lanes 0..31 and share the tile's columns; warp 5 (more
-    // than 32 token rows) reads lanes 32..63.  A lane holds one token's row of the partial sum.
-    const int row = (warp == 5 ? 32 : 0) + lane;
+  } else if (warp == 0 || warp == 4 || (warp == 5 && p.tok_rows > (p.mma_rows == 64 ? 16 : 32))) {
+    // Warps 0 and 4 may both read TMEM lanes 0..31 and share the tile's columns; warp 5 reads
+    // lanes 32..63.  A lane holds one token's row of the partial sum: row = lane for a
+    // 128-row product; a 64-row product keeps rows 16 q .. 16 q + 15 in the first 16 lanes of
+    // lane quarter q, so rows 16..31 are warp 5's.
+    const bool narrow = p.mma_rows == 64;
+    const int per = narrow ? 16 : 32;                      // rows a lane quarter holds
+    const int row = lane < per ? (warp == 5 ? per : 0) + lane : 1 << 20;
     const uint32_t lanes = (uint32_t)(warp == 5 ? 32 : 0) << 16;
     const int width = kAct ? p.bn / 2 : p.bn;          // columns to walk: outputs or sums
     const int chunks = (width + 15) / 16, half = (chunks + 1) / 2;
@@ -292,7 +295,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     // (SwiGLU form) the factor of this lane's row, worked out while the products run
     float factor = 1.f;
     if (kAct && p.rs.partials)
-      for (int t = (warp == 5 ? 32 : 0); t < p.tokens && t < (warp == 5 ? 64 : 32); ++t) {
+      for (int t = (warp == 5 ? per : 0); t < p.tokens && t < (warp == 5 ? 2 * per : per); ++t) {
         const float ft = bf_row_factor(p.rs, t, lane);
         if (t == row) factor = ft;
       }
@@ -565,13 +568,14 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   p.stages = stages;
   static const int issuers = getenv("BINFER_B200_GEMM_ISSUERS") ? atoi(getenv("BINFER_B200_GEMM_ISSUERS")) : 2;
   p.issuers = issuers == 1 ? 1 : 2;
-  // With at most 16 token rows (rows 0..15 lie in tensor memory lanes 0..15 for both shapes)
-  // a 64-row product does: half the tensor work per weight byte.  The time of one product is
+  // With at most 32 token rows (a 64-row product keeps rows 0..15 in tensor memory lanes
+  // 0..15 and rows 16..31 in lanes 32..47) a 64-row product does: half the tensor work per
+  // weight byte.  The time of one product is
   // the same, but a decode step is long enough to run into the board's power limit, and with
   // 128-row products for 8 tokens the SM clock settled near 1750 MHz instead of 1965 (36
   // layers, batch 8: 4.28 against 4.12 ms a step with every projection on this kernel).
   static const int rows = getenv("BINFER_B200_GEMM_MMA_ROWS") ? atoi(getenv("BINFER_B200_GEMM_MMA_ROWS")) : 64;
-  p.mma_rows = rows == 64 && p.tok_rows <= 16 ? 64 : 128;
+  p.mma_rows = rows == 64 && p.tok_rows <= 32 ? 64 : 128;
   int need = p.issuers * p.bn, cols = 32;
   while (cols < need) cols *= 2;
   p.tmem_cols = cols;

@@ -7,7 +7,7 @@ makes for every dense product (cuda/kernels/gemm.cu:244-267: ``cublasGemmEx``, b
 in, ``CUBLAS_COMPUTE_32F``).  Which one: ``BINFER_B200_GEMM=own`` takes the engine's
 kernel for every shape it accepts, ``library`` never, and ``auto`` (the default)
 where it was measured to be at least as fast as the library on a B200: at most 128
-tokens against a very wide weight (the output head while decoding), and at most 16
+tokens against a very wide weight (the output head while decoding), and at most 32
 tokens against a weight of at most 8192 output features, where the split-K cluster
 kernel (``csrc/gemm_tcgen05_cluster.cu``) runs (the qkv, output and down projections).
 Alone, the cluster kernel ties with the library on the qkv projection; inside a decode
@@ -44,9 +44,10 @@ def _use_own(M: int, N: int, K: int) -> bool:
 
 
 def _use_cluster(M: int, N: int, K: int) -> bool:
-    # the kernel takes up to 64 tokens, but from 32 on the library is faster inside a step
-    # (8 layers: 1.764 against 1.739 ms at 32 tokens, 2.585 against 2.448 ms at 64)
-    if _POLICY == "library" or M > (16 if _POLICY == "auto" else ops.CLUSTER_MAX_TOKENS):
+    # the kernel takes up to 64 tokens, but beyond 32 (where its products have 128 rows
+    # instead of 64) the library is faster inside a step: all 36 layers, 6.14 against 5.98 ms
+    # at 24 tokens, 6.96 against 6.97 at 32, 10.20 against 10.89 at 64 (library against own)
+    if _POLICY == "library" or M > cluster_token_limit():
         return False
     # wider weights (the gate/up projection, on "clusters" of one CTA) measured 2 us slower
     # per call than the library inside a decode step
@@ -62,7 +63,7 @@ def cluster_token_limit() -> int:
     """Most token rows for which the policy sends products to the split-K cluster kernel."""
     if _POLICY == "library":
         return 0
-    return 16 if _POLICY == "auto" else ops.CLUSTER_MAX_TOKENS
+    return 32 if _POLICY == "auto" else ops.CLUSTER_MAX_TOKENS
 
 
 _plans = {}
@@ -120,7 +121,7 @@ def linear_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
     """``resid += x @ w^T`` with the next RMSNorm prepared in the same kernel: returns
     ``(bfloat16(resid * norm_w), ops.RowScale)``, the norm's output short of the factor
     ``rsqrt(mean(resid^2) + eps)`` per row, or None, having done nothing, where the cluster
-    kernel does not run (float32, more than 16 tokens, shapes without a plan)."""
+    kernel does not run (float32, more than 32 tokens, shapes without a plan)."""
     M, (N, K) = x.shape[0], w.shape
     if (not FUSE_NORM or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
             or not _use_cluster(M, N, K)):

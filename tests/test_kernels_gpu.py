@@ -288,7 +288,8 @@ def test_decode_attention_more_splits_than_one_merge_pass(cuda_device, variant, 
 
 @pytest.mark.parametrize("M,N,K,bn,c", [(8, 4096, 4096, 128, 4), (3, 200, 512, 64, 2),
                                         (16, 1000, 320, 80, 1), (64, 4096, 4096, 128, 4),
-                                        (37, 1024, 2048, 64, 4)])
+                                        (37, 1024, 2048, 64, 4), (27, 520, 1024, 64, 2),
+                                        (32, 4096, 4096, 128, 4)])
 def test_gemm_cluster_adds_into_the_stream_and_prepares_the_norm(cuda_device, M, N, K, bn, c):
     """resid += x w^T in float; xt = bf16(resid * norm_w); the partial sums of squares add up
     to the rows' sums, so that xt times the factor is the RMSNorm of the new stream."""
@@ -327,6 +328,7 @@ def test_gemm_cluster_adds_into_the_stream_and_prepares_the_norm(cuda_device, M,
     (13, 5, 1, 96, 64, 1280, 192, 4, True, True),        # a rotation over part of the head
     (16, 3, 3, 256, 256, 512, 256, 1, False, False),     # one CTA a tile, no head norms
     (37, 7, 1, 128, 0, 2304, 128, 5, True, True),        # token rows beyond 32, no rotation
+    (21, 4, 2, 64, 64, 1024, 128, 2, True, True),        # 17 to 32 token rows
     (2, 4, 0, 128, 128, 640, 256, 2, True, False),       # queries only: another layer's pages
     (1, 8, 2, 32, 0, 768, 32, 3, False, True),           # fewer tokens than CTAs in a cluster
 ])
@@ -408,6 +410,7 @@ def test_gemm_cluster_qkv_plan_keeps_whole_heads(cuda_device):
     (5, 1000, 512, 0, False),         # outputs that are no multiple of the tile
     (16, 2504, 320, 48, True),        # 24 outputs a tile: the last chunk of a tile is cut
     (37, 264, 1024, 256, True),       # token rows beyond 32; one tile holds part of the outputs
+    (29, 1000, 512, 0, True),         # 17 to 32 token rows: 64-row products, two lane quarters
     (1, 4480, 1536, 112, False),
 ])
 def test_gemm_swiglu_matches_product_then_activation(cuda_device, T, I, K, bn, scaled):
