@@ -3,7 +3,6 @@ ship, defined here: a mixer with state of its own, a feed-forward with routing, 
 position encoding, a schedule that runs a layer twice and lets a layer read another's pages.
 None of them needs a change to the framework's files."""
 from dataclasses import dataclass
-from typing import Optional
 
 import pytest
 import torch
@@ -132,11 +131,10 @@ class DecaySpec:
 
 def _register_toy_parts():
     """A mixer with fixed-size state per request (an exponentially decaying sum of the
-    projected inputs), a feed-forward with top-1 routing over two experts, and a position
-    encoding that adds a learned vector per position bucket; plain tensor code, float32."""
+    projected inputs) and a feed-forward with top-1 routing over two experts; plain tensor
+    code, float32.  (The position encodings: ``_register_toy_positions``.)"""
     from binfer_b200.cache import StateNeed
-    from binfer_b200.parts import (FeedForward, Mixer, register_ffn, register_mixer,
-                                   register_position)
+    from binfer_b200.parts import FeedForward, Mixer, register_ffn, register_mixer
     from binfer_b200.weights import ParamSpec
 
     class DecayMixer(Mixer):
