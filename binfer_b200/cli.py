@@ -30,6 +30,7 @@ VALUE_FLAGS = {
 BOOL_FLAGS = {
     "--chat", "--bench", "--profile", "--no-cache", "-q", "--quiet", "--help", "-h",
     "--verbose", "-v", "--no-cuda-graphs", "--use-template", "--ignore-eos",
+    "--allow-unexpected-tensors",
 }
 
 USAGE = """
@@ -61,7 +62,9 @@ Options:
   -i, --input <file>       Input file with prompts (one per line), processed in batch
   -o, --output <file>      Output file for batch results (one per line)
   --random-weights <seed>  Draw random weights for the folder's config.json (no safetensors needed)
-  --kv-memory-gb <f>       Memory for the key/value cache (default: 10)
+  --allow-unexpected-tensors  Warn about tensors the model does not use instead of refusing
+  --kv-memory-gb <f>       Memory for the key/value cache (default: 0.9 of what is free
+                           after loading, at most max-batch-size x max-seq-len tokens)
   --kv-pages <n>           Size of the cache in pages instead
   --page-size <n>          Tokens per cache page (default: 64)
   --max-tokens-per-step <n>  Token budget of one step (default: 2048)
@@ -111,7 +114,7 @@ def parse_args(argv: List[str]) -> dict:
              bench=False, profile=False, trace=None, quiet=False, verbose=False, cuda_graphs=True,
              temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=None,
              ignore_eos=False, input=None, output=None, use_template=False, random_weights=None,
-             kv_memory_gb=10.0, kv_pages=None, page_size=64, max_tokens_per_step=2048,
+             kv_memory_gb=None, kv_pages=None, allow_unexpected_tensors=False, page_size=64, max_tokens_per_step=2048,
              max_seq_len=4096, max_batch_size=64)
     names = {"--max-tokens": ("max_tokens", int), "--tp": ("tp", str), "--dtype": ("dtype", str),
              "-p": ("prompt", str), "--prompt": ("prompt", str), "--prompt-ids": ("prompt", str),
@@ -126,7 +129,8 @@ def parse_args(argv: List[str]) -> dict:
              "--max-seq-len": ("max_seq_len", int), "--max-batch-size": ("max_batch_size", int)}
     flags = {"--chat": "chat", "--bench": "bench", "--profile": "profile", "-q": "quiet",
              "--quiet": "quiet", "-v": "verbose", "--verbose": "verbose",
-             "--use-template": "use_template", "--ignore-eos": "ignore_eos"}
+             "--use-template": "use_template", "--ignore-eos": "ignore_eos",
+             "--allow-unexpected-tensors": "allow_unexpected_tensors"}
     i = 0
     while i < len(argv):
         t = argv[i]
@@ -238,13 +242,15 @@ def main(argv: Optional[List[str]] = None) -> int:
         if args["random_weights"] is not None:
             engine = Engine(load_config(model), random_seed=args["random_weights"], **kw)
         else:
-            engine = Engine(model, **kw)
+            engine = Engine(model, allow_unexpected_tensors=args["allow_unexpected_tensors"],
+                            **kw)
     except (ValueError, FileNotFoundError, RuntimeError) as e:
         print(f"Error: {e}", file=sys.stderr)
         return 1
+    engine.warm_up()                  # the decode graphs, before the first request
     t_loaded = time.perf_counter()
     if args["verbose"]:
-        log(f"  startup: {t_loaded - t_start:.2f}s (model + cache on device)")
+        log(f"  startup: {t_loaded - t_start:.2f}s (model + cache on device, decode graphs)")
     tokens = _Tokens(model)
     prof = Profiler(engine) if (args["profile"] or args["trace"]) else None
     sampling = dict(max_tokens=args["max_tokens"], temperature=args["temperature"],

@@ -168,20 +168,22 @@ class Qwen3Config:
             bad = sorted(set(self.layer_types) - {"full_attention", "sliding_attention"})
             if bad:
                 raise ConfigError(f"unknown layer_types entries: {bad}")
-        sliding = self.use_sliding_window or (
-            self.layer_types is not None and "sliding_attention" in self.layer_types)
-        if sliding and not (self.sliding_window and self.sliding_window > 0):
-            raise ConfigError("sliding attention layers need a positive sliding_window")
+        if self.use_sliding_window and not (self.sliding_window and self.sliding_window > 0):
+            raise ConfigError("use_sliding_window needs a positive sliding_window")
 
     # ------------------------------------------------------------- derivation
     def layer_windows(self) -> List[Optional[int]]:
         """Window of each layer, ``None`` where a layer sees every earlier key.
 
-        ``layer_types`` decides when present.  Otherwise, with
-        ``use_sliding_window``, layers from ``max_window_layers`` on are
-        windowed (the first ``max_window_layers`` keep full attention).
+        Without ``use_sliding_window`` no layer has a window, whatever ``layer_types``
+        and ``sliding_window`` say (the architecture's own configuration drops the window
+        then, so its ``sliding_attention`` layers attend to every key).  With it,
+        ``layer_types`` decides when present; otherwise layers from ``max_window_layers``
+        on are windowed (the first ``max_window_layers`` keep full attention).
         """
         n = self.num_hidden_layers
+        if not self.use_sliding_window:
+            return [None] * n
         if self.layer_types is not None:
             return [self.sliding_window if t == "sliding_attention" else None
                     for t in self.layer_types]

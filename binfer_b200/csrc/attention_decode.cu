@@ -51,6 +51,9 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ q,
   const int p = positions[t];
   const int j0 = window > 0 ? max(0, p - window + 1) : 0;
   const int k_begin = split * DEC_SPLIT;
+  // the grid has max_splits splits: keys beyond them have nowhere to put their partial
+  if (split == 0 && g == 0 && threadIdx.x == 0 && p / DEC_SPLIT >= max_splits)
+    atomicOr(err, BF_ERR_SPLITS);
   if (k_begin > p || k_begin + DEC_SPLIT <= j0) return;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -286,7 +289,8 @@ decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
   }
   const int p = positions[t];
   const int j0 = window > 0 ? max(0, p - window + 1) : 0;
-  const int s_first = j0 / DEC_SPLIT, n = p / DEC_SPLIT - s_first + 1;
+  // never beyond the scratch: the attention kernel has flagged a row that needs more splits
+  const int s_first = j0 / DEC_SPLIT, n = min(p / DEC_SPLIT, max_splits - 1) - s_first + 1;
   const float2* ml = ml2 + s_first;
   float M = -INFINITY;
   for (int k0 = 0; k0 < n; k0 += MERGE_CLASSES * UA) {
@@ -334,7 +338,7 @@ decode_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
     acc.w += __shfl_xor_sync(0xffffffffu, acc.w, d);
   }
   if (sc == 0) {
-    const float inv = 1.f / L;
+    const float inv = n > 0 ? 1.f / L : 0.f;
     uint2 packed;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
     o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
@@ -355,7 +359,8 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
   const size_t smem_max = tiles + merge;
   const size_t smem = nh / nkv <= 16 ? tiles : smem_max;
   auto kern = decode_attention_split_kernel<D>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem_max);
@@ -378,7 +383,9 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
   return bf_launch_status();
 }
 
-// max_splits must be >= ceil(longest context / 128) of the rows given.
+// max_splits must be >= ceil(longest context / 128) of the rows given; a row that needs more
+// sets BF_ERR_SPLITS in the error word, and the splits beyond the scratch are left out (no
+// kernel reads or writes past part_o / part_ml).
 // Returns cudaErrorInvalidValue for head sizes it does not take (take the generic kernel).
 BF_EXPORT int bf_decode_attention(const void* q, const void* k_cache, const void* v_cache,
                                   const int* rows, const int* seq_of_token, const int* positions,

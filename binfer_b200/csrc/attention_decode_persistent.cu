@@ -196,7 +196,12 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
         t = rows ? rows[r] : r;
         p = positions[t];
         const int j0 = window > 0 ? max(0, p - window + 1) : 0;
-        cnt = (p / DP_SPLIT - j0 / DP_SPLIT + 1) * nkv;
+        int last = p / DP_SPLIT;
+        if (last >= max_splits) {        // splits without room in the scratch get no item
+          atomicOr(err, BF_ERR_SPLITS);
+          last = max_splits - 1;
+        }
+        cnt = max(0, last - j0 / DP_SPLIT + 1) * nkv;
       }
       int incl = cnt;
 #pragma unroll
@@ -516,7 +521,8 @@ static int launch_persistent(const void* q, const void* k_cache, const void* v_c
   e = bf_make_tensor_map_bf16_2d(&mv, v_cache, cache_rows, D, D, page_size, 64);
   if (e) return e;
   auto kern = decode_attention_persistent_kernel<D>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t ce =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit);

@@ -49,6 +49,9 @@ extern "C" {
 // rows (may be null: rows 0..n_rows-1), seq_of_token, positions: int32 per token;
 // block_tables int32 [requests, table_stride]; out [tokens, nh, d] bf16;
 // max_splits >= ceil(longest context / 128); err: int32 error word on the device.
+// A row whose keys need more splits than max_splits says is not a fault: the kernels set
+// bit 16 of the error word, leave the splits without room out of that row's result, and
+// neither read nor write past the part of the array that the call was sized for.
 // Returns 0, a BF_STATIC_ERR_* code (negative), or a cudaError_t (positive).
 int bf_decode_attention_static(const void* q, const void* k_cache, const void* v_cache,
                                const int* rows, const int* seq_of_token, const int* positions,

@@ -60,6 +60,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   const int p = positions[t];
   const int j0 = window > 0 ? max(0, p - window + 1) : 0;
   const int k_begin = split * DT_SPLIT;
+  // the grid has max_splits splits: keys beyond them have nowhere to put their partial
+  if (split == 0 && g == 0 && threadIdx.x == 0 && p / DT_SPLIT >= max_splits)
+    atomicOr(err, BF_ERR_SPLITS);
   if (k_begin > p || k_begin + DT_SPLIT <= j0) return;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -279,7 +282,8 @@ static int launch_tma(const void* q, const void* k_cache, const void* v_cache, c
   const size_t smem_max = 1024 + tiles + 16 + merge;
   const size_t smem = nh / nkv <= 16 ? 1024 + tiles + 16 : smem_max;
   auto kern = decode_attention_tma_kernel<D>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem_max);

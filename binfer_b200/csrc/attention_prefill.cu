@@ -215,7 +215,8 @@ static int launch_prefill(const void* q, const void* k_cache, const void* v_cach
   constexpr int LD = D + 8;
   const size_t smem = (size_t)4 * PF_BN * LD * 2 + 2 * PF_BN * 8;
   auto kern = prefill_attention_kernel<D>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);

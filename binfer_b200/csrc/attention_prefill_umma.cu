@@ -412,7 +412,8 @@ int launch_umma(const void* q, const void* k_cache, const void* v_cache, const i
   const size_t smem = 1024 + (size_t)HALVES * 16384 + (size_t)4 * HALVES * 8192 +
                       (HALVES * 8192 >= 16384 ? 0 : 16384) + 3 * 1024 + 128;
   auto kern = prefill_attention_umma_kernel<D>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem);

@@ -476,7 +476,8 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
   const size_t smem = 1024 + (size_t)2 * 32768 + (size_t)2 * A2_STAGES * 16384 +
                       (size_t)2 * 16384 + 2 * 3 * 1024 + 256;
   auto kern = prefill_attention_umma2_kernel;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem);

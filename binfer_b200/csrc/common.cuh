@@ -17,6 +17,7 @@
 #define BF_ERR_SLOT 2          // cache slot outside the pool
 #define BF_ERR_PAGE 4          // page id outside the pool
 #define BF_ERR_WAIT 8          // a bounded wait gave up
+#define BF_ERR_SPLITS 16       // a row's keys need more splits than the scratch has room for
 
 #define BF_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -55,6 +56,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int bf_launch_status() { return (int)cudaGetLastError(); }
+
+// Function attributes (the dynamic shared memory limit) belong to a device, so launchers keep
+// their "configured" flag per device: index of the current one, clamped to the table.
+#define BF_MAX_DEVICES 64
+static inline int bf_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+  return dev < BF_MAX_DEVICES ? dev : BF_MAX_DEVICES - 1;
+}
 
 // ---------------------------------------------------- programmatic dependent launch
 // A kernel launched through bf_launch_pdl may be scheduled while its predecessor on the

@@ -277,7 +277,8 @@ int launch(const void* x, const void* w, OutT* out, GemmParams p, long long ldx,
   p.stages = stages;
   const size_t smem = fixed + (size_t)stages * stage_bytes;
   auto kern = gemm_tcgen05_kernel<OutT>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem_max);

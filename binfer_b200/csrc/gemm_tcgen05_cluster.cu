@@ -587,7 +587,8 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   size_t smem = fixed + (size_t)stages * stage_bytes;
   if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = gemm_cluster_kernel<OutT, FORM>;
-  static bool configured = false;
+  static bool configured_on[BF_MAX_DEVICES];
+  bool& configured = configured_on[bf_current_device()];
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem_max);

@@ -238,12 +238,16 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      rows: Optional[torch.Tensor], n_rows: int, seq_of_token: torch.Tensor,
                      positions: torch.Tensor, block_tables: torch.Tensor, out: torch.Tensor,
                      nh: int, nkv: int, d: int, window: Optional[int], scale: float,
-                     max_ctx_len: int, err: torch.Tensor, variant: str = "auto") -> None:
+                     max_ctx_len: int, err: torch.Tensor, variant: str = "auto",
+                     scratch=None) -> None:
     """Split-KV attention for rows that bring one token each (bfloat16 only).
 
     ``rows`` lists the token rows to run (None: rows 0..n_rows-1); ``max_ctx_len``
-    bounds the context of every such row.  Scratch for the splits' partial results
-    is taken from torch's allocator.  ``variant``: ``persistent`` (resident CTAs that walk
+    bounds the context of every such row (a row beyond it sets the error word's
+    "splits" bit and loses its far keys; nothing is read or written past the scratch).
+    Scratch for the splits' partial results is taken from torch's allocator, or given as
+    ``scratch = (part_o [n_rows, nh, splits, d], part_ml [n_rows, nh, splits, 2])`` float32,
+    whose ``splits`` then is the room there is.  ``variant``: ``persistent`` (resident CTAs that walk
     the work with a ring of TMA-fed tiles; head sizes 64/128/256, page sizes 8..128 that
     divide 128, at most 16 query heads per kv head and 512 rows), ``tma`` (one CTA per split,
     bulk tensor copies; the same head and page sizes), ``cp_async`` (every size in
@@ -268,9 +272,18 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         name, fn = "decode_attention_tma", lib().bf_decode_attention_tma
     else:
         name, fn = "decode_attention", lib().bf_decode_attention
-    max_splits = max(1, -(-int(max_ctx_len) // DECODE_SPLIT_KEYS))
-    part_o = torch.empty((n_rows, nh, max_splits, d), dtype=torch.float32, device=q.device)
-    part_ml = torch.empty((n_rows, nh, max_splits, 2), dtype=torch.float32, device=q.device)
+    if scratch is None:
+        max_splits = max(1, -(-int(max_ctx_len) // DECODE_SPLIT_KEYS))
+        part_o = torch.empty((n_rows, nh, max_splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_rows, nh, max_splits, 2), dtype=torch.float32, device=q.device)
+    else:
+        part_o, part_ml = scratch
+        max_splits = part_o.shape[2]
+        _want(part_o, torch.float32, "part_o"); _want(part_ml, torch.float32, "part_ml")
+        if (tuple(part_o.shape) != (n_rows, nh, max_splits, d)
+                or tuple(part_ml.shape) != (n_rows, nh, max_splits, 2)):
+            raise KernelError("decode_attention: scratch must be [n_rows, nh, splits, d] and "
+                              "[n_rows, nh, splits, 2]")
     _run(name, fn,
          _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(rows), _ptr(seq_of_token), _ptr(positions),
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _ptr(part_o),

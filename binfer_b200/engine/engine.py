@@ -1,8 +1,9 @@
 """The Python entry point: ``Engine(model).generate(prompt_ids, ...)``.
 
 Option names follow the reference's engine options and generate call
-(src/engine/batched_engine.ts:3224-3240: ``maxKvMemoryGB`` 10, ``maxSeqLen`` 4096,
-``maxBatchSize`` 64, ``cudaGraphs``; :3133-3203: ``generate(ids, maxNewTokens,
+(src/engine/batched_engine.ts:3224-3240: ``maxKvMemoryGB``, ``maxSeqLen`` 4096,
+``maxBatchSize`` 64, ``cudaGraphs``; the cache's default size is the server's, a share of
+the memory that is free once the weights are loaded, src/serve.ts:987-1002; :3133-3203: ``generate(ids, maxNewTokens,
 onToken, sampling)`` returns the generated ids, the stop token included, and stops
 early when the callback returns false).  Unlike the reference's ``generate``, which
 serves one request and reserves pages for prompt + max tokens at once (:3144), any
@@ -28,16 +29,24 @@ from .scheduler import FINISHED, PENDING, Request, Scheduled, Scheduler
 class Engine:
     def __init__(self, model: Union[str, object], dtype: str = "bfloat16", *,
                  random_seed: Optional[int] = None, random_std: float = 0.02,
-                 max_kv_memory_gb: float = 10.0, num_pages: Optional[int] = None,
+                 max_kv_memory_gb: Optional[float] = None, num_pages: Optional[int] = None,
+                 gpu_memory_utilization: float = 0.9,
                  page_size: int = 64, max_seq_len: int = 4096, max_batch_size: int = 64,
                  max_tokens_per_step: int = 2048, cuda_graphs: bool = True,
-                 look_ahead: bool = True, device: str = "cuda:0"):
+                 look_ahead: bool = True, device: str = "cuda:0",
+                 allow_unexpected_tensors: bool = False):
         """``model``: a folder with config.json and safetensors, or (with
-        ``random_seed``) a typed configuration whose weights are drawn on the device."""
+        ``random_seed``) a typed configuration whose weights are drawn on the device.
+
+        The cache's size: ``num_pages`` pages per cache group, else ``max_kv_memory_gb``,
+        else ``gpu_memory_utilization`` of the device memory that is free once the weights
+        are loaded (less 2 GB for activations, logits and graphs), and never more than
+        ``max_batch_size`` requests of ``max_seq_len`` tokens can use."""
         self.env = make_env(dtype, device)
         if isinstance(model, str):
             self.config = load_config(model)
-            self.model = model_from_dir(model, self.env)
+            self.model = model_from_dir(model, self.env,
+                                        allow_unexpected=allow_unexpected_tensors)
         else:
             if random_seed is None:
                 raise ValueError("a configuration without a folder needs random_seed")
@@ -50,7 +59,13 @@ class Engine:
             esize = 2 if self.env.dtype == torch.bfloat16 else 4
             per_page = sum(2 * n.num_kv_heads * n.head_dim * page_size * esize
                            for n in kv_needs if n is not None)
-            num_pages = max(1, int(max_kv_memory_gb * (1 << 30)) // max(per_page, 1))
+            if max_kv_memory_gb is not None:
+                budget = int(max_kv_memory_gb * (1 << 30))
+            else:
+                free, _ = torch.cuda.mem_get_info(self.env.device)
+                budget = int(free * gpu_memory_utilization) - (2 << 30)
+            most = max_batch_size * (-(-self.max_seq_len // page_size) + 1)
+            num_pages = max(1, min(budget // max(per_page, 1), most))
         cache = CacheManager(kv_needs, self.model.state_needs(), page_size=page_size,
                              num_pages=num_pages, max_requests=max_batch_size)
         self.runner = ModelRunner(self.model, cache, self.env)
@@ -83,6 +98,26 @@ class Engine:
         self.scheduler.add(req)
         self.requests[rid] = req
         return rid
+
+    def warm_up(self) -> None:
+        """Capture the decode step's CUDA graph for every batch bucket now, so that no
+        request pays for a capture.  (The reference captures after five warm-up calls of a
+        batch size, inside generation: src/engine/batched_engine.ts:1813-1830.)  Runs one
+        padded single-token step per bucket on a scratch request and frees it again."""
+        if not self.cuda_graphs or self.has_work():
+            return
+        rid = ("warm-up", next(self._ids))
+        self.runner.add_request(rid)
+        try:
+            for _ in range(2 * len(self.runner._buckets)):
+                missing = [b for b in self.runner._buckets if b not in self.runner._graphs
+                           or self.runner._graphs[b]["graph"] is None]
+                if not missing:
+                    break
+                self.runner.step([StepItem(rid, [0], [0])], bucket=missing[0])
+        finally:
+            self.runner.free_request(rid)
+        torch.cuda.synchronize()
 
     def abort(self, rid: Hashable) -> None:
         self.scheduler.abort(self.requests[rid])
@@ -185,13 +220,21 @@ class Engine:
         single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
         batch = [prompts] if single else list(prompts)
         rids = []
-        for i, p in enumerate(batch):
-            params = SamplingParams(
-                temperature=temperature, top_k=top_k, top_p=top_p,
-                repetition_penalty=repetition_penalty,
-                seed=None if seed is None else seed + i, max_tokens=max_tokens,
-                ignore_eos=ignore_eos)
-            rids.append(self.add_request(p, params, eos_ids=eos_ids))
+        try:
+            for i, p in enumerate(batch):
+                params = SamplingParams(
+                    temperature=temperature, top_k=top_k, top_p=top_p,
+                    repetition_penalty=repetition_penalty,
+                    seed=None if seed is None else seed + i, max_tokens=max_tokens,
+                    ignore_eos=ignore_eos)
+                rids.append(self.add_request(p, params, eos_ids=eos_ids))
+        except Exception:
+            # a refused prompt takes the call's earlier prompts with it: nothing of this
+            # call may stay queued and run beside a later one
+            for rid in rids:
+                self.abort(rid)
+                self.requests.pop(rid, None)
+            raise
         index = {rid: i for i, rid in enumerate(rids)}
         told = {rid: 0 for rid in rids}          # tokens of each request already reported
 

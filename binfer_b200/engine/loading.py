@@ -46,11 +46,11 @@ def make_env(dtype: Union[str, torch.dtype], device: Union[str, torch.device] = 
     return BuildEnv(parse_dtype(dtype), device)
 
 
-def model_from_dir(model_dir: str, env: BuildEnv) -> DecoderModel:
+def model_from_dir(model_dir: str, env: BuildEnv, allow_unexpected: bool = False) -> DecoderModel:
     config = load_config(model_dir)
     source = TensorSource.from_dir(model_dir)
     try:
-        return build_model(config.to_spec(), env, source)
+        return build_model(config.to_spec(), env, source, allow_unexpected=allow_unexpected)
     finally:
         source.close()
 

@@ -249,11 +249,13 @@ class ModelRunner:
         for rid, new_len in wants:
             self.cache.reserve(rid, new_len)
 
-    def step(self, items: Sequence[StepItem],
-             device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem], device_ids: Optional[torch.Tensor] = None,
+             bucket: Optional[int] = None) -> torch.Tensor:
         """Run the items as one batch; logits ``[R, vocab]`` float32 on the device, in
         the order of the items and of each item's ``want``.  ``device_ids``: int32 ids on
-        the device from which items with ``src_row`` take their token."""
+        the device from which items with ``src_row`` take their token.  ``bucket``: run a
+        step of single tokens from the graph of this batch bucket (a larger one than the
+        items need: how the graphs are captured ahead of the first request)."""
         if not items:
             raise ValueError("a step needs at least one item")
         seen = set()
@@ -268,7 +270,7 @@ class ModelRunner:
             self.cache.zero_fresh_state(self.cache.get(it.rid))
         new_lens = [self.cache.get(it.rid).length + len(it.tokens) for it in items]
         if self._can_replay(items, new_lens):
-            logits = self._graph_step(items, device_ids)
+            logits = self._graph_step(items, device_ids, bucket)
         else:
             ctx = self.build_context(items, device_ids=device_ids)
             logits = self.model.forward(ctx, self.views)
@@ -300,10 +302,13 @@ class ModelRunner:
                 and all(len(it.tokens) == 1 for it in items)
                 and max(new_lens) <= self._graph_seq_len)
 
-    def _graph_step(self, items: Sequence[StepItem],
-                    device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _graph_step(self, items: Sequence[StepItem], device_ids: Optional[torch.Tensor] = None,
+                    bucket: Optional[int] = None) -> torch.Tensor:
         B = len(items)
-        bucket = next(b for b in self._buckets if b >= B)
+        if bucket is None:
+            bucket = next(b for b in self._buckets if b >= B)
+        elif bucket not in self._buckets or bucket < B:
+            raise ValueError(f"no graph bucket {bucket} for {B} items")
         widths = [-(-self._graph_seq_len // g.page_size) for g in self.cache.groups]
         st = self._graphs.get(bucket)
         if st is None:
@@ -345,5 +350,7 @@ class ModelRunner:
             what = [name for bit, name in ((1, "token id outside the vocabulary"),
                                            (2, "cache slot outside the pool"),
                                            (4, "page id outside the pool or already released"),
-                                           (8, "a bounded wait gave up")) if code & bit]
+                                           (8, "a bounded wait gave up"),
+                                           (16, "a row's context needs more key splits than "
+                                                "the attention scratch holds")) if code & bit]
             raise StepError("kernel error: " + "; ".join(what))

@@ -63,10 +63,12 @@ class DecoderModel:
             specs.append(self.head_spec)
         return specs
 
-    def load(self, source: TensorSource) -> None:
-        """Check every name and shape first (one error for all), then take the tensors."""
+    def load(self, source: TensorSource, allow_unexpected: bool = False) -> None:
+        """Check every name and shape first (one error for all), then take the tensors.
+        ``allow_unexpected``: tensors the model does not use are a warning, not an error."""
         optional = [self.spec.names.lm_head] if self.head_spec is None else []
-        check_names(self.param_specs(), source.shapes, optional=optional, where=source.where)
+        check_names(self.param_specs(), source.shapes, optional=optional, where=source.where,
+                    allow_unexpected=allow_unexpected)
 
         def get(spec: ParamSpec) -> torch.Tensor:
             return place(source.get(spec.name), spec, self.env.dtype, self.env.device)
@@ -145,7 +147,8 @@ def param_specs_for(spec: ModelSpec) -> List[ParamSpec]:
     return DecoderModel(spec, env).param_specs()
 
 
-def build_model(spec: ModelSpec, env: BuildEnv, source: TensorSource) -> DecoderModel:
+def build_model(spec: ModelSpec, env: BuildEnv, source: TensorSource,
+                allow_unexpected: bool = False) -> DecoderModel:
     model = DecoderModel(spec, env)
-    model.load(source)
+    model.load(source, allow_unexpected=allow_unexpected)
     return model

@@ -8,11 +8,17 @@ up front which names and shapes it needs (:class:`ParamSpec`), and
 together.
 
 File discovery follows src/loader/mmap_loader.ts:88-107: ``model.safetensors`` if
-it exists, else every ``*.safetensors`` in the folder, sorted.
+it exists, else every ``*.safetensors`` in the folder, sorted.  Unlike the
+reference, ``model.safetensors.index.json`` is read when it is there: the model is
+then exactly the shards that its ``weight_map`` names; a shard that is missing is
+one error that names it, and a ``*.safetensors`` file that the index does not
+name is left alone, with a warning.
 """
 from __future__ import annotations
 
+import json
 import os
+import warnings
 from dataclasses import dataclass
 from typing import Callable, Dict, Iterable, List, Mapping, Optional, Tuple
 
@@ -51,22 +57,57 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+INDEX_FILE = "model.safetensors.index.json"
+
+
+def read_index(model_dir: str) -> Optional[Dict[str, str]]:
+    """``weight_map`` (tensor name -> shard file) of the folder's index, or None without one."""
+    path = os.path.join(model_dir, INDEX_FILE)
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        index = json.load(f)
+    wm = index.get("weight_map")
+    if not isinstance(wm, dict) or not wm:
+        raise ValueError(f"{path} has no weight_map")
+    return {str(k): str(v) for k, v in wm.items()}
+
+
 def find_safetensors_files(model_dir: str) -> List[str]:
-    single = os.path.join(model_dir, "model.safetensors")
-    if os.path.exists(single):
-        return [single]
-    files = sorted(f for f in os.listdir(model_dir) if f.endswith(".safetensors"))
-    if not files:
+    """The files that hold the model.  With an index: its shards, all of which must exist
+    (one error names every missing one); files the index does not name are ignored, with a
+    warning.  Without: ``model.safetensors``, else every ``*.safetensors``, sorted."""
+    present = sorted(f for f in os.listdir(model_dir) if f.endswith(".safetensors"))
+    index = read_index(model_dir)
+    if index is not None:
+        shards = sorted(set(index.values()))
+        gone = [f for f in shards if not os.path.exists(os.path.join(model_dir, f))]
+        if gone:
+            raise FileNotFoundError(
+                f"{model_dir}: {INDEX_FILE} names shards that are not there "
+                f"({len(gone)} of {len(shards)}): " + ", ".join(gone))
+        extra = [f for f in present if f not in shards]
+        if extra:
+            warnings.warn(f"{model_dir}: ignoring safetensors files that {INDEX_FILE} does not "
+                          f"name: " + ", ".join(extra))
+        return [os.path.join(model_dir, f) for f in shards]
+    if "model.safetensors" in present:
+        return [os.path.join(model_dir, "model.safetensors")]
+    if not present:
         raise FileNotFoundError(f"No safetensors files found in {model_dir}")
-    return [os.path.join(model_dir, f) for f in files]
+    return [os.path.join(model_dir, f) for f in present]
 
 
 def check_names(specs: Iterable[ParamSpec], found: Mapping[str, Tuple[int, ...]],
-                optional: Iterable[str] = (), where: str = "") -> None:
+                optional: Iterable[str] = (), where: str = "",
+                allow_unexpected: bool = False) -> None:
     """Raise :class:`WeightError` unless ``found`` (name -> shape) is exactly ``specs``.
 
     Names in ``optional`` may be present without being asked for (a stored
-    ``lm_head.weight`` beside tied embeddings, for instance).
+    ``lm_head.weight`` beside tied embeddings, for instance).  With
+    ``allow_unexpected`` tensors that nobody asked for are named in a warning instead
+    of the error (the reference uploads them silently, src/loader/mmap_loader.ts:175-225);
+    missing tensors and wrong shapes are an error either way.
     """
     want = {s.name: tuple(s.shape) for s in specs}
     optional = set(optional)
@@ -74,6 +115,11 @@ def check_names(specs: Iterable[ParamSpec], found: Mapping[str, Tuple[int, ...]]
     unexpected = sorted(n for n in found if n not in want and n not in optional)
     wrong = sorted((n, tuple(found[n]), want[n]) for n in want
                    if n in found and tuple(found[n]) != want[n])
+    if allow_unexpected and unexpected and not (missing or wrong):
+        warnings.warn(f"checkpoint {where}: ignoring {len(unexpected)} tensors the model does "
+                      f"not use: " + ", ".join(unexpected[:20])
+                      + (" ..." if len(unexpected) > 20 else ""))
+        return
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where)
 
@@ -88,6 +134,14 @@ class Checkpoint:
         for f in self.files:
             for n in f.names():
                 self._where[n] = f
+        index = read_index(model_dir)
+        if index is not None:
+            # the index is the model's own list: a tensor it names must be in the shard it names
+            by_path = {os.path.basename(f.path): f for f in self.files}
+            lost = sorted(n for n, shard in index.items() if n not in by_path[shard].infos)
+            if lost:
+                raise WeightError(lost, [], [], where=f"{model_dir} (tensors that {INDEX_FILE} "
+                                                     f"names are not in their shards)")
 
     def shapes(self) -> Dict[str, Tuple[int, ...]]:
         return {n: f.infos[n].shape for n, f in self._where.items()}

@@ -69,6 +69,17 @@ TINY_F = dict(
     use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
     attention_bias=False)
 
+# the layer sizes of the Qwen3-8B shape (hidden 4096, 32/8 heads of 128, 12288 inner
+# features, an untied head over 151936 words) with fewer layers: two.  What a decode or a
+# prefill step of the full model launches, kernel for kernel, but small enough to compare
+# with the plain implementation.
+QWEN3_8B_TWO_LAYERS = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+    vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu",
+    attention_bias=False)
+
 TINY = {
     "O": dict(raw=TINY_O, std=0.03, norm_std=0.05, page_size=64, seed=77),
     "V": dict(raw=TINY_V, std=0.05, norm_std=0.02, page_size=32, seed=66),
@@ -186,6 +197,22 @@ def trace_mixed(reqs: Dict[str, List[int]], max_live: int = 4, tail: int = 10,
         live = [r for r in live if r[2] < len(r[1])]
         s += 1
     return steps
+
+
+def thin_wants(steps: List[dict], keep) -> List[dict]:
+    """The same steps with logits wanted only where ``keep(request, position)`` says so."""
+    pos: Dict[str, int] = {}
+    out = []
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            a = pos.get(e["id"], 0)
+            entries.append(dict(e, want=[w for w in e["want"] if keep(e["id"], a + w)]))
+            pos[e["id"]] = a + len(e["tokens"])
+        for rid in st["end"]:
+            pos.pop(rid, None)
+        out.append(dict(st, entries=entries))
+    return out
 
 
 def peak_pages(steps: List[dict], page_size: int) -> int:

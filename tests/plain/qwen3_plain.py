@@ -43,9 +43,12 @@ def read_config(raw: dict) -> dict:
     sc = raw.get("rope_scaling")
     if sc and sc.get("rope_type", sc.get("type")) == "linear":
         c["factor"] = float(sc["factor"])
-    # windows: layer_types wins; else layers from max_window_layers on are windowed
+    # windows only with use_sliding_window; then layer_types wins, else layers from
+    # max_window_layers on are windowed
     n, w = c["layers"], raw.get("sliding_window")
-    if raw.get("layer_types"):
+    if not raw.get("use_sliding_window"):
+        c["windows"] = [None] * n
+    elif raw.get("layer_types"):
         c["windows"] = [w if t == "sliding_attention" else None for t in raw["layer_types"]]
     elif raw.get("use_sliding_window") and w:
         first = raw.get("max_window_layers") or 0
@@ -53,6 +56,13 @@ def read_config(raw: dict) -> dict:
     else:
         c["windows"] = [None] * n
     return c
+
+
+# A model of the reference's bfloat16 arithmetic, for error bounds: every function below
+# computes in the working precision; ``_r(x, rt)`` then rounds a result to ``rt`` (bfloat16)
+# wherever the reference's kernels store one in bfloat16 (with ``rt`` None, nowhere).
+def _r(x: torch.Tensor, rt: Optional[torch.dtype]) -> torch.Tensor:
+    return x if rt is None else x.to(rt).to(x.dtype)
 
 
 # ------------------------------------------------------------------------- parts
@@ -111,57 +121,68 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
 
 
 def attention_block(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, c: dict,
-                    positions: torch.Tensor, window: Optional[int]) -> torch.Tensor:
+                    positions: torch.Tensor, window: Optional[int],
+                    rt: Optional[torch.dtype] = None) -> torch.Tensor:
     """q,k,v projections, per-head RMSNorm of q and k with the layer norms' eps, then
     the rotation, attention and the output projection
     (src/engine/batched_engine.ts:811-839,861-876,1061-1090,1116-1118)."""
     T = x.shape[0]
     nh, nkv, d = c["heads"], c["kv_heads"], c["head_dim"]
-    q = (x @ w[prefix + "q_proj.weight"].T).view(T, nh, d)
-    k = (x @ w[prefix + "k_proj.weight"].T).view(T, nkv, d)
-    v = (x @ w[prefix + "v_proj.weight"].T).view(T, nkv, d)
-    q = rms_norm(q, w[prefix + "q_norm.weight"], c["eps"])
-    k = rms_norm(k, w[prefix + "k_norm.weight"], c["eps"])
+    q = _r(x @ w[prefix + "q_proj.weight"].T, rt).view(T, nh, d)
+    k = _r(x @ w[prefix + "k_proj.weight"].T, rt).view(T, nkv, d)
+    v = _r(x @ w[prefix + "v_proj.weight"].T, rt).view(T, nkv, d)
+    q = _r(rms_norm(q, w[prefix + "q_norm.weight"], c["eps"]), rt)
+    k = _r(rms_norm(k, w[prefix + "k_norm.weight"], c["eps"]), rt)
     ang = rope_angles(positions, d, c["theta"], c["factor"])
-    q, k = apply_rope(q, ang), apply_rope(k, ang)
-    a = causal_attention(q, k, v, 1.0 / math.sqrt(d), window)      # batched_engine.ts:1062
-    return a.reshape(T, nh * d) @ w[prefix + "o_proj.weight"].T
+    q, k = _r(apply_rope(q, ang), rt), _r(apply_rope(k, ang), rt)
+    a = _r(causal_attention(q, k, v, 1.0 / math.sqrt(d), window), rt)   # batched_engine.ts:1062
+    return _r(a.reshape(T, nh * d) @ w[prefix + "o_proj.weight"].T, rt)
 
 
-def swiglu_mlp(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def swiglu_mlp(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str,
+               rt: Optional[torch.dtype] = None) -> torch.Tensor:
     """down( silu(gate(x)) * up(x) ), silu(g) = g / (1 + exp(-g))
     (src/engine/batched_engine.ts:1243-1265; cuda/kernels/bf16_kernels.cu:461-477)."""
-    g = x @ w[prefix + "gate_proj.weight"].T
-    u = x @ w[prefix + "up_proj.weight"].T
-    return ((g / (1.0 + torch.exp(-g))) * u) @ w[prefix + "down_proj.weight"].T
+    g = _r(x @ w[prefix + "gate_proj.weight"].T, rt)
+    u = _r(x @ w[prefix + "up_proj.weight"].T, rt)
+    return _r(_r((g / (1.0 + torch.exp(-g))) * u, rt) @ w[prefix + "down_proj.weight"].T, rt)
 
 
 def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, c: dict,
-                  positions: torch.Tensor) -> torch.Tensor:
+                  positions: torch.Tensor, rt: Optional[torch.dtype] = None) -> torch.Tensor:
     """Pre-norm residual block: x + attn(norm(x)), then x + mlp(norm(x))
-    (src/engine/batched_engine.ts:800-1314)."""
+    (src/engine/batched_engine.ts:800-1314; the sums are formed in float and stored in
+    the activations' type, cuda/kernels/bf16_kernels.cu:504-517)."""
     p = f"model.layers.{i}."
-    n = rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
-    x = x + attention_block(n, w, p + "self_attn.", c, positions, c["windows"][i])
-    n = rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
-    return x + swiglu_mlp(n, w, p + "mlp.")
+    n = _r(rms_norm(x, w[p + "input_layernorm.weight"], c["eps"]), rt)
+    x = _r(x + attention_block(n, w, p + "self_attn.", c, positions, c["windows"][i], rt), rt)
+    n = _r(rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), rt)
+    return _r(x + swiglu_mlp(n, w, p + "mlp.", rt), rt)
 
 
 def forward(raw_config: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int],
-            dtype: torch.dtype = torch.float32) -> torch.Tensor:
+            dtype: torch.dtype = torch.float32,
+            rows: Optional[Sequence[int]] = None,
+            round_to: Optional[torch.dtype] = None) -> torch.Tensor:
     """Logits ``[T, vocab]`` at every position of one whole sequence
     (final norm and head: src/engine/batched_engine.ts:1733-1770; the head is the
-    embedding table when ``tie_word_embeddings``, :1753-1755)."""
+    embedding table when ``tie_word_embeddings``, :1753-1755).  ``rows``: only these
+    positions' logits (the layers still run the whole sequence).  ``round_to``
+    (bfloat16): every result that the reference stores in bfloat16, the logits
+    included (:2609), is rounded to it: a model of the reference's own rounding,
+    against which the engine's bfloat16 error can be held."""
     c = read_config(raw_config)
     w = {k: t.to(dtype) for k, t in weights.items()}
     ids_t = torch.as_tensor(list(ids), dtype=torch.long)
     positions = torch.arange(len(ids_t))
     x = embedding(ids_t, w["model.embed_tokens.weight"])
     for i in range(c["layers"]):
-        x = decoder_layer(x, w, i, c, positions)
-    x = rms_norm(x, w["model.norm.weight"], c["eps"])
+        x = decoder_layer(x, w, i, c, positions, round_to)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
+    x = _r(rms_norm(x, w["model.norm.weight"], c["eps"]), round_to)
     head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
-    return x @ head.T
+    return _r(x @ head.T, round_to)
 
 
 # ---------------------------------------------------------------------- sampling

@@ -64,6 +64,13 @@ def test_windows_per_layer():
     assert c2.layer_windows() == [None, 8]
     c3 = Qwen3Config.from_dict({**H.TINY_A, "sliding_window": 8})     # not switched on
     assert c3.layer_windows() == [None, None]
+    # layer_types that name sliding layers, but the switch is off: every layer attends fully
+    c4 = Qwen3Config.from_dict({**H.TINY_W, "use_sliding_window": False})
+    assert c4.layer_windows() == [None] * 4
+    assert all(l.mixer.window is None for l in c4.to_spec().layers)
+    import qwen3_plain as P
+    assert P.read_config({**H.TINY_W, "use_sliding_window": False})["windows"] == [None] * 4
+    assert P.read_config(H.TINY_W)["windows"] == [None, 24, 24, None]
 
 
 def test_spec_is_chosen_layer_by_layer():

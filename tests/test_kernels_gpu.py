@@ -286,6 +286,32 @@ def test_decode_attention_more_splits_than_one_merge_pass(cuda_device, variant, 
     _close(out, ref, BF16)
 
 
+@pytest.mark.parametrize("variant", ["cp_async", "tma", "persistent"])
+def test_decode_attention_flags_a_row_beyond_its_scratch(cuda_device, variant):
+    """Scratch with room for one split and a row of 200 keys, which needs two: the error
+    word's bit says so, nothing behind the scratch is touched, and the row that fits is
+    right all the same."""
+    from binfer_b200.csrc import ops
+    nh, nkv, d, ps = 8, 2, 128, 16
+    ctxs = [200, 90]
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   [1, 1], None, seed=21)
+    cells = len(ctxs) * nh * 1
+    buf = torch.full((cells * (d + 2) + 8192,), 777.0, dtype=torch.float32, device=cuda_device)
+    part_o = buf[:cells * d].view(len(ctxs), nh, 1, d)
+    part_ml = buf[cells * d:cells * (d + 2)].view(len(ctxs), nh, 1, 2)
+    out = torch.zeros_like(q)
+    err = _err(cuda_device)
+    ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, None,
+                         d ** -0.5, max(ctxs), err, variant=variant, scratch=(part_o, part_ml))
+    torch.cuda.synchronize()
+    assert int(err.item()) == 16
+    err.zero_()
+    assert bool((buf[cells * (d + 2):] == 777.0).all()), "memory behind the scratch was written"
+    _close(out[1], ref[1], BF16)
+    assert bool(torch.isfinite(out.float()).all())
+
+
 @pytest.mark.parametrize("M,N,K,bn,c", [(8, 4096, 4096, 128, 4), (3, 200, 512, 64, 2),
                                         (16, 1000, 320, 80, 1), (64, 4096, 4096, 128, 4),
                                         (37, 1024, 2048, 64, 4), (27, 520, 1024, 64, 2),

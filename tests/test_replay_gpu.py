@@ -276,3 +276,39 @@ def test_long_context_bfloat16(cuda_device, plain_logits):
     got = H.run_trace(runner, steps)
     worst = max(H.rel_err(row, ref["long"][pos]) for (rid, pos), row in got.items())
     assert len(got) == 44 and worst <= TOL[dtype], worst
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_logits_alone_and_in_company(cuda_device, plain_logits, dtype):
+    """A request decodes ten tokens alone, and again with a 39-token portion of another
+    request's prompt in each of its steps.  float32: the same bits (every sum's order depends
+    on the position only).  bfloat16: which kernel runs a product depends on how many tokens
+    the step holds (the split-K cluster kernels up to 32 tokens, the library beyond; decode
+    and prefill attention kernels), so the bits differ; the logits agree within the bound
+    that both are held to against the plain implementation."""
+    which = "F"
+    vocab = H.TINY[which]["raw"]["vocab_size"]
+    reqs = {"a": H.random_tokens(70, vocab, 5), "b": H.random_tokens(39 * 10, vocab, 6)}
+    model_dir, ref = plain_logits(which, dtype, reqs)
+    a, b = reqs["a"], reqs["b"]
+    first = {"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": [59]}], "end": []}
+    alone, company = [first], [dict(first)]
+    for i in range(10):
+        last = i == 9
+        alone.append({"step": i + 1, "entries": [{"id": "a", "tokens": [a[60 + i]], "want": [0]}],
+                      "end": ["a"] if last else []})
+        company.append({"step": i + 1, "entries": [
+            {"id": "b", "tokens": b[39 * i:39 * (i + 1)], "want": [38]},
+            {"id": "a", "tokens": [a[60 + i]], "want": [0]}], "end": ["a", "b"] if last else []})
+    ps = H.TINY[which]["page_size"]
+    outs = [H.run_trace(_runner(model_dir, dtype, ps, H.peak_pages(st, ps)), st)
+            for st in (alone, company)]
+    for key, row in outs[0].items():
+        assert H.rel_err(row, ref[key[0]][key[1]]) <= TOL[dtype]
+        other = outs[1][key]
+        if dtype == torch.float32:
+            assert torch.equal(row, other), f"float32 logits at {key} depend on the company"
+        else:
+            assert H.rel_err(other, row) <= TOL[dtype], f"logits at {key} differ in company"
+    for key, row in outs[1].items():
+        assert H.rel_err(row, ref[key[0]][key[1]]) <= TOL[dtype]

@@ -142,3 +142,22 @@ def test_random_workloads_finish_and_free_everything(seed):
         if r.finish_reason == "length":
             assert len(r.output) == r.params.max_tokens
     assert cache.num_free_pages() == [cache.num_pages] and not cache.requests
+
+
+def test_generate_leaves_nothing_queued_when_a_prompt_is_refused():
+    """A good prompt followed by an empty one: the call raises, and the good prompt does not
+    stay behind to run beside the next call's requests."""
+    import itertools
+    from types import SimpleNamespace
+    from binfer_b200.engine.engine import Engine
+    eng = Engine.__new__(Engine)          # the request bookkeeping only: no device, no model
+    cache = CacheManager([KVNeed(2, 16)], page_size=8, num_pages=16, max_requests=4)
+    eng.scheduler = Scheduler(cache, max_running=4, max_tokens_per_step=64, max_model_len=64)
+    eng.spec = SimpleNamespace(vocab_size=100, eos_token_ids=(2,))
+    eng.requests, eng._ids, eng._pending = {}, itertools.count(), None
+    with pytest.raises(RequestRefused):
+        eng.generate([[1, 2, 3], []], max_tokens=4)
+    assert not eng.scheduler.has_work() and not eng.requests
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.generate([[1, 2, 3], [4, 100]], max_tokens=4)
+    assert not eng.scheduler.has_work() and not eng.requests

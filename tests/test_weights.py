@@ -121,3 +121,53 @@ def test_loading_a_wrong_checkpoint_fails_before_anything_is_taken(tmp_path):
         model.load(TensorSource.from_dict(w))
     assert "up_proj" in str(e.value) and "extra.bias" in str(e.value) and "[8]" in str(e.value)
     assert model.embed is None
+
+
+def test_index_names_the_shards(tmp_path):
+    """With model.safetensors.index.json the model is the shards it names: a missing shard
+    is one error that names it, a file it does not name is ignored with a warning, and a
+    tensor it names must be in its shard."""
+    import warnings
+    from binfer_b200.weights.loader import find_safetensors_files
+    a = {"x": torch.randn(2, 2), "y": torch.randn(3)}
+    b = {"z": torch.randn(4)}
+    save_file(a, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file(b, str(tmp_path / "model-00002-of-00002.safetensors"))
+    index = {"metadata": {}, "weight_map": {"x": "model-00001-of-00002.safetensors",
+                                            "y": "model-00001-of-00002.safetensors",
+                                            "z": "model-00002-of-00002.safetensors"}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    src = TensorSource.from_dir(str(tmp_path))
+    assert set(src.shapes) == {"x", "y", "z"} and torch.equal(src.get("z"), b["z"])
+    src.close()
+    # a stale file beside the shards is not part of the model
+    save_file({"old": torch.zeros(1)}, str(tmp_path / "leftover.safetensors"))
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        src = TensorSource.from_dir(str(tmp_path))
+        src.close()
+    assert "old" not in src.shapes and any("leftover.safetensors" in str(x.message) for x in w)
+    # a tensor the index promises but the shard lacks
+    index["weight_map"]["gone"] = "model-00002-of-00002.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightError, match="gone"):
+        TensorSource.from_dir(str(tmp_path))
+    # a shard that is not there
+    os.remove(str(tmp_path / "model-00002-of-00002.safetensors"))
+    with pytest.raises(FileNotFoundError, match="model-00002-of-00002.safetensors"):
+        find_safetensors_files(str(tmp_path))
+
+
+def test_unexpected_tensors_can_be_a_warning():
+    import warnings
+    specs = [ParamSpec("a", (2, 3))]
+    with pytest.raises(WeightError, match="unexpected tensors"):
+        check_names(specs, {"a": (2, 3), "buffer": (1,)})
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        check_names(specs, {"a": (2, 3), "buffer": (1,)}, allow_unexpected=True)
+    assert any("buffer" in str(x.message) for x in w)
+    # what is missing or misshapen stays an error, and the error still lists the extras
+    with pytest.raises(WeightError) as e:
+        check_names(specs, {"a": (3, 2), "buffer": (1,)}, allow_unexpected=True)
+    assert "buffer" in str(e.value) and "expected [2, 3]" in str(e.value)

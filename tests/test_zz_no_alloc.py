@@ -70,6 +70,33 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(cuda_device):
         assert int(err.item()) == 0
         _close(got, want.double().cpu(), BF16)     # against the existing entry point
         _close(got, ref, BF16)                     # and against the plain reference
+        # a subset of the rows, named by index: those rows get the same bits, the others nothing
+        rows = torch.tensor([2, 0], dtype=torch.int32, device=cuda_device)
+        some = torch.zeros_like(q)
+        code = _call_static(lib, q, kc, vc, rows, 2, sot, pos, bt, some, nh, nkv, d, window,
+                            max_splits, err)
+        assert code == 0, _message(lib, code)
+        torch.cuda.synchronize()
+        assert torch.equal(some[2], got[2]) and torch.equal(some[0], got[0])
+        assert float(some[1].abs().max()) == 0.0
+
+
+def test_static_scratch_entry_point_flags_too_few_splits(cuda_device):
+    """max_splits is the caller's word; a row whose keys need more than it says sets the
+    error word's bit 16 and loses its far keys, instead of reading or writing past the
+    room the call was sized for."""
+    from binfer_b200.csrc import ops
+    lib = ops.lib()
+    nh, nkv, d, ps = 8, 2, 128, 16
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, [200, 90],
+                                                   [1, 1], None, seed=2)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out = torch.zeros_like(q)
+    code = _call_static(lib, q, kc, vc, None, 2, sot, pos, bt, out, nh, nkv, d, None, 1, err)
+    assert code == 0, _message(lib, code)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 16
+    _close(out[1], ref[1], BF16)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit(cuda_device):
