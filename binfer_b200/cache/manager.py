@@ -75,6 +75,35 @@ class RequestCache:
         return arr[:n]
 
 
+def plan_pages(kv_needs: Sequence[Optional[KVNeed]], page_size: int, budget_bytes: int,
+               element_size: int, max_requests: int, max_seq_len: int,
+               max_tokens_per_step: int):
+    """Share ``budget_bytes`` out among the cache groups; returns ``need -> pages`` for
+    :class:`CacheManager`.
+
+    A group that keeps every key needs ``max_seq_len`` tokens per request at most; a windowed
+    one needs its window plus the longest portion a step may write (pages behind the window
+    are given back before a step's new ones are taken) plus a page's slack at either end.
+    Groups get pages in proportion to those needs, the windowed ones never more than
+    ``max_requests`` requests can use; what that saves goes to the others.  (The reference
+    has one pool, every layer alike: src/kv/paged.ts:55-62.)"""
+    per_request, page_bytes = {}, {}
+    for need in kv_needs:
+        if need is None:
+            continue
+        key = need.group_key
+        tokens = max_seq_len if need.window is None else min(
+            max_seq_len, need.window + max_tokens_per_step)
+        per_request[key] = -(-tokens // page_size) + 2
+        page_bytes[key] = page_bytes.get(key, 0) + (
+            2 * need.num_kv_heads * need.head_dim * page_size * element_size)
+    # pages per unit of "request": scale every group's need by the same factor f
+    unit = sum(per_request[k] * page_bytes[k] for k in per_request)
+    f = min(float(max_requests), budget_bytes / unit) if unit else 0.0
+    pages = {k: max(1, int(f * per_request[k])) for k in per_request}
+    return lambda need: pages[need.group_key]
+
+
 class CacheGroup:
     def __init__(self, index: int, need: KVNeed, num_pages: int, page_size: int):
         self.index = index
@@ -98,11 +127,14 @@ class CacheManager:
 
     def __init__(self, kv_needs: Sequence[Optional[KVNeed]],
                  state_needs: Sequence[Optional[StateNeed]] = (),
-                 page_size: int = 16, num_pages: int = 64, max_requests: int = 64):
+                 page_size: int = 16, num_pages=64, max_requests: int = 64):
+        """``num_pages``: pages of every group's pool, or a function of a group's
+        :class:`KVNeed` that gives its pool's pages (a windowed group keeps far fewer keys
+        per request than one that keeps them all: see :func:`plan_pages`)."""
         if page_size < 1:
             raise ValueError("page_size must be positive")
         self.page_size = int(page_size)
-        self.num_pages = int(num_pages)
+        pages_of = num_pages if callable(num_pages) else (lambda need: int(num_pages))
         self.groups: List[CacheGroup] = []
         # schedule entry -> (group index, index of the entry inside its group)
         self.entry_location: List[Optional[Tuple[int, int]]] = []
@@ -113,11 +145,13 @@ class CacheManager:
                 continue
             g = by_key.get(need.group_key)
             if g is None:
-                g = CacheGroup(len(self.groups), need, num_pages, self.page_size)
+                g = CacheGroup(len(self.groups), need, int(pages_of(need)), self.page_size)
                 by_key[need.group_key] = g
                 self.groups.append(g)
             self.entry_location.append((g.index, len(g.entries)))
             g.entries.append(e)
+        # the largest pool (what a request that keeps every key can draw on)
+        self.num_pages = max([g.pool.num_pages for g in self.groups], default=0)
         self.state_needs = list(state_needs) + [None] * (len(kv_needs) - len(state_needs))
         self.slots = SlotPool(max_requests)
         self.requests: Dict[Hashable, RequestCache] = {}
@@ -223,6 +257,17 @@ class CacheManager:
     def pages_for_tokens(self, n: int) -> int:
         """Pages one full-attention group needs for ``n`` tokens (src/kv/paged.ts:180)."""
         return -(-n // self.page_size)
+
+    def can_ever_hold(self, n: int) -> bool:
+        """Whether a lone request of ``n`` tokens fits every group's pool: all of its pages
+        where every key is kept, its window's pages (and the one being written) elsewhere,
+        where a long prompt can always come in short portions."""
+        for g in self.groups:
+            w = g.need.window
+            need = -(-n // g.page_size) if w is None else -(-min(n, w + 1) // g.page_size) + 1
+            if need > g.pool.num_pages:
+                return False
+        return True
 
     def check_consistent(self) -> None:
         """Every page is either free or held by exactly one live request."""

@@ -17,7 +17,7 @@ from typing import Callable, Dict, Hashable, List, Optional, Sequence, Union
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, plan_pages
 from ..config.registry import load_config
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -57,15 +57,14 @@ class Engine:
         kv_needs = self.model.kv_needs()
         if num_pages is None:
             esize = 2 if self.env.dtype == torch.bfloat16 else 4
-            per_page = sum(2 * n.num_kv_heads * n.head_dim * page_size * esize
-                           for n in kv_needs if n is not None)
             if max_kv_memory_gb is not None:
                 budget = int(max_kv_memory_gb * (1 << 30))
             else:
                 free, _ = torch.cuda.mem_get_info(self.env.device)
-                budget = int(free * gpu_memory_utilization) - (2 << 30)
-            most = max_batch_size * (-(-self.max_seq_len // page_size) + 1)
-            num_pages = max(1, min(budget // max(per_page, 1), most))
+                budget = max(0, int(free * gpu_memory_utilization) - (2 << 30))
+            # per group: a windowed group gets the pages its window needs, not the full pool's
+            num_pages = plan_pages(kv_needs, page_size, budget, esize, max_batch_size,
+                                   self.max_seq_len, max_tokens_per_step)
         cache = CacheManager(kv_needs, self.model.state_needs(), page_size=page_size,
                              num_pages=num_pages, max_requests=max_batch_size)
         self.runner = ModelRunner(self.model, cache, self.env)

@@ -97,10 +97,10 @@ class Scheduler:
         if n + 1 > self.max_model_len:
             raise RequestRefused(f"request {req.rid!r}: prompt of {n} tokens exceeds "
                                  f"max_model_len {self.max_model_len}")
-        if self.cache.pages_for_tokens(n + 1) > self.cache.num_pages:
+        if not self.cache.can_ever_hold(n + 1):
             raise RequestRefused(f"request {req.rid!r}: prompt of {n} tokens can never fit "
-                                 f"the cache ({self.cache.num_pages} pages of "
-                                 f"{self.cache.page_size})")
+                                 f"the cache ({[g.pool.num_pages for g in self.cache.groups]} "
+                                 f"pages of {self.cache.page_size} per group)")
         req.state = WAITING
         self.waiting.append(req)
 

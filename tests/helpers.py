@@ -80,7 +80,17 @@ QWEN3_8B_TWO_LAYERS = dict(
     use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu",
     attention_bias=False)
 
+# for the smoke test: small, but of the sizes that a decode step's tcgen05 kernels take
+# (2048 inputs to every projection, heads of 128, a head product over more than 65536 words)
+SMOKE_WIDE = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=2048,
+    num_attention_heads=16, num_key_value_heads=4, head_dim=128, intermediate_size=3072,
+    vocab_size=66001, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
+    use_sliding_window=False, max_position_embeddings=4096, hidden_act="silu",
+    attention_bias=False)
+
 TINY = {
+    "S": dict(raw=SMOKE_WIDE, std=0.02, norm_std=0.05, page_size=64, seed=88),
     "O": dict(raw=TINY_O, std=0.03, norm_std=0.05, page_size=64, seed=77),
     "V": dict(raw=TINY_V, std=0.05, norm_std=0.02, page_size=32, seed=66),
     "F": dict(raw=TINY_F, std=0.03, norm_std=0.05, page_size=64, seed=55),
@@ -121,6 +131,21 @@ def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
 def rel_rms(got: torch.Tensor, ref: torch.Tensor) -> float:
     d = (got.double() - ref.double())
     return float(d.pow(2).mean().sqrt() / ref.double().pow(2).mean().sqrt())
+
+
+def assert_greedy_within_rounding(raw, w, prompts, outs, bound=3e-2):
+    """Every generated token is the plain implementation's choice at its place, given the
+    tokens before it, or, where the plain logits of the best tokens lie closer together than
+    bfloat16 rounding can tell apart (``bound`` of the largest logit), one of those."""
+    import qwen3_plain as P
+    for p, out in zip(prompts, outs):
+        logits = P.forward(raw, w, list(p) + list(out), dtype=torch.float64)
+        for n, tok in enumerate(out):
+            row = logits[len(p) - 1 + n]
+            slack = bound * float(row.abs().max())
+            assert float(row[tok]) >= float(row.max()) - slack, (
+                f"token {n} of a prompt of {len(p)}: {tok} has plain logit {float(row[tok]):.4f}, "
+                f"the best ({int(row.argmax())}) {float(row.max()):.4f}")
 
 
 # ------------------------------------------------------------------------ traces

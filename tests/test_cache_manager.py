@@ -143,3 +143,48 @@ def test_random_orders_lose_no_page(seed):
         m.free_request(rid)
     assert m.num_free_pages() == [g.pool.num_pages for g in m.groups]
     assert m.slots.num_free == 5
+
+
+def test_groups_get_pools_of_their_own_size():
+    """A windowed group keeps a window's worth of keys per request, so its pool is planned
+    smaller than the pool of a group that keeps every key; the bytes it saves buy the other
+    group more pages."""
+    from binfer_b200.cache.manager import plan_pages
+    full, win = KVNeed(2, 16), KVNeed(2, 16, window=32)
+    needs = [full, win, win, full]
+    page = 2 * 2 * 16 * 8 * 4                       # one page of one layer, float32
+    budget = 40 * page * 4                          # 40 pages for every layer, were all alike
+    pages = plan_pages(needs, page_size=8, budget_bytes=budget, element_size=4, max_requests=4,
+                       max_seq_len=256, max_tokens_per_step=16)
+    n_full, n_win = pages(full), pages(win)
+    assert n_win < n_full and n_full > 40
+    assert 2 * page * (n_full + n_win) <= budget
+    # never more than the requests can use
+    roomy = plan_pages(needs, 8, 10 ** 12, 4, max_requests=4, max_seq_len=256,
+                       max_tokens_per_step=16)
+    assert roomy(full) == 4 * (256 // 8 + 2) and roomy(win) == 4 * ((32 + 16) // 8 + 2)
+    cm = CacheManager(needs, page_size=8, num_pages=pages, max_requests=4)
+    assert [g.pool.num_pages for g in cm.groups] == [n_full, n_win]
+    assert cm.num_pages == n_full
+    # a long lone request fits if the full group can hold it; the windowed group only needs
+    # its window (and the page being written)
+    assert cm.can_ever_hold(n_full * 8) and not cm.can_ever_hold(n_full * 8 + 1)
+    small = CacheManager([win], page_size=8, num_pages=4, max_requests=2)
+    assert not small.can_ever_hold(1000)            # window 32 -> 5 pages + 1
+    assert CacheManager([win], page_size=8, num_pages=6, max_requests=2).can_ever_hold(1000)
+
+
+def test_a_windowed_request_runs_through_a_small_pool():
+    """Far more tokens than the pool holds pass through a windowed group, portion by portion,
+    because pages behind the window come back before a step takes new ones."""
+    cm = CacheManager([KVNeed(1, 8, window=20)], page_size=4, num_pages=9, max_requests=1)
+    cm.add_request("r")
+    n = 0
+    for step in range(60):
+        n += 7
+        assert cm.can_reserve([("r", n)])
+        cm.reserve("r", n)
+        cm.commit("r", n)
+        cm.check_consistent()
+    cm.free_request("r")
+    assert cm.groups[0].pool.num_held == 0

@@ -93,20 +93,6 @@ def test_preemption_recomputes_the_same_tokens(cuda_device, tmp_path):
     assert tight.stats()["pages_free"] == tight.stats()["pages_total"]
 
 
-def assert_greedy_within_rounding(raw, w, prompts, outs, bound=3e-2):
-    """Every generated token is the plain implementation's choice at its place, given the
-    tokens before it, or, where the plain logits of the best tokens lie closer together than
-    bfloat16 rounding can tell apart (``bound`` of the largest logit), one of those."""
-    for p, out in zip(prompts, outs):
-        logits = P.forward(raw, w, list(p) + list(out), dtype=torch.float64)
-        for n, tok in enumerate(out):
-            row = logits[len(p) - 1 + n]
-            slack = bound * float(row.abs().max())
-            assert float(row[tok]) >= float(row.max()) - slack, (
-                f"token {n} of a prompt of {len(p)}: {tok} has plain logit {float(row[tok]):.4f}, "
-                f"the best ({int(row.argmax())}) {float(row.max()):.4f}")
-
-
 def test_bfloat16_generation_matches_plain_within_rounding(cuda_device, tmp_path):
     """bfloat16, graphs and eager: the same tokens both ways, and tokens that the plain
     implementation (float64, on the same stored weights) also ranks first, up to what
@@ -118,7 +104,7 @@ def test_bfloat16_generation_matches_plain_within_rounding(cuda_device, tmp_path
     b = _engine(d, "bfloat16", cuda_graphs=False).generate(prompts, max_tokens=16, ignore_eos=True)
     assert all(len(x) == 16 for x in a)
     assert a == b
-    assert_greedy_within_rounding(raw, w, prompts, a)
+    H.assert_greedy_within_rounding(raw, w, prompts, a)
 
 
 def test_warm_up_captures_the_decode_graphs_before_the_first_request(cuda_device, tmp_path):
