@@ -2,8 +2,8 @@
 tiny random models, so that an accidental change of the oracle itself is noticed.
 
 The numbers come from the plain implementation alone (float64 on the CPU).  The
-reference's own model code cannot be run for them: it is TypeScript for Bun over CUDA
-kernels, and neither Bun nor a GPU exists where the tests are written.
+reference's model code cannot be run as a whole (TypeScript for Bun over CUDA kernels);
+numbers from its kernels, part by part, are made by make_reference_kernel_golden.py.
 
     python tests/golden/make_golden.py
 """

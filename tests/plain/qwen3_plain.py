@@ -4,11 +4,14 @@ This is the tests' oracle.  It shares no code with ``binfer_b200``: it reads the
 raw config.json dictionary and a name -> tensor dictionary itself, and runs on
 the CPU with ordinary tensor arithmetic.
 
-It rests on the reference's formulas, not on its execution: bwasti/binfer's model
-code is TypeScript for Bun (``bun:ffi``) over CUDA kernels and cuBLAS, and neither
-Bun nor a GPU exists where these tests are written, so nothing of it can be
-imported or compiled on the CPU.  Each function cites the file and lines of the
-reference that it restates (paths inside the bwasti/binfer project).
+Nothing of bwasti/binfer's model code can be imported or compiled on a CPU: it is
+TypeScript for Bun (``bun:ffi``) over CUDA kernels and cuBLAS.  So each function
+restates the reference's formulas and cites the file and lines it restates (paths
+inside the bwasti/binfer project).  The parts are also held to the reference's
+execution: its kernel files compile unmodified for sm_100a, and what they made of
+small inputs on a B200 is committed under ``tests/golden/`` with the script that
+ran them; ``tests/test_plain_against_reference_kernels.py`` compares every part
+here with those numbers.
 
 ``dtype`` is the working precision (float32 by default; float64 gives an oracle
 whose own rounding is negligible).  Rotation angles are always formed in
@@ -139,13 +142,17 @@ def attention_block(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, c:
     return _r(a.reshape(T, nh * d) @ w[prefix + "o_proj.weight"].T, rt)
 
 
+def silu_mul(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    """silu(g) * u with silu(g) = g / (1 + exp(-g)) (cuda/kernels/bf16_kernels.cu:461-477)."""
+    return (g / (1.0 + torch.exp(-g))) * u
+
+
 def swiglu_mlp(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str,
                rt: Optional[torch.dtype] = None) -> torch.Tensor:
-    """down( silu(gate(x)) * up(x) ), silu(g) = g / (1 + exp(-g))
-    (src/engine/batched_engine.ts:1243-1265; cuda/kernels/bf16_kernels.cu:461-477)."""
+    """down( silu(gate(x)) * up(x) ) (src/engine/batched_engine.ts:1243-1265)."""
     g = _r(x @ w[prefix + "gate_proj.weight"].T, rt)
     u = _r(x @ w[prefix + "up_proj.weight"].T, rt)
-    return _r(_r((g / (1.0 + torch.exp(-g))) * u, rt) @ w[prefix + "down_proj.weight"].T, rt)
+    return _r(_r(silu_mul(g, u), rt) @ w[prefix + "down_proj.weight"].T, rt)
 
 
 def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, c: dict,
