@@ -2,6 +2,8 @@
 """Benchmark: decode tokens per second of the Qwen3-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --shape 32b            # the Qwen3-32B shape: batch 1/8/32 to context 8192
+    python bench.py --workload serve       # continuous batching, the Qwen3-1.7B shape
 
 Default run: the layer sizes of the Qwen3-8B shape with random weights in
 bfloat16, a batch of 8 requests decoding at a context of 4096 tokens.  A "step"
@@ -17,11 +19,20 @@ is one decode step (one new token per request).  One JSON line is printed with
   measured bf16 peak;
 - ``roofline``: bytes the decode step must read (every weight once, the cache of
   the live requests) over its time, against the measured copy bandwidth;
-- ``points``: decode tokens per second at batch 1 and 64;
+- ``points``: decode tokens per second at batch 1 and 64, at batch 8 and 64 with
+  16-token pages (the reference's block size; the engine's default page is 64 tokens), and
+  the output tokens per second of the continuous-batching workload below;
 - ``clocks``: SM clock and throttle reasons sampled during the timed region.
 
 Between timed steps the inputs (15 GB of weights, gigabytes of cache) are far
 larger than the 126 MB L2, so no explicit flush is needed.
+
+``--workload serve``: 64 requests with prompts of 128 to 2048 tokens (uniform, seeded) and
+256 output tokens each, all submitted at once to ``Engine.add_request`` and driven by
+``Engine.step`` (scheduler, mixed steps of prompt portions beside decode tokens, admission
+and page churn) on the Qwen3-1.7B shape: output and total tokens per second, mean time to
+the first token, mean time between tokens, preemptions, and how the wall time splits
+between the host inside ``Engine.step`` and the GPU.
 """
 import argparse
 import json
@@ -41,6 +52,14 @@ QWEN3_8B = dict(
     intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
     tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu",
     attention_bias=False, use_sliding_window=False)
+QWEN3_1P7B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=2048, num_attention_heads=16,
+                  num_key_value_heads=8, intermediate_size=6144, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                 num_key_value_heads=8, intermediate_size=25600)
+# shape -> (config, name, context of the decode points, batches: the second is the headline)
+SHAPES = {"8b": (QWEN3_8B, "Qwen3-8B", 4096, (1, 8, 64)),
+          "1.7b": (QWEN3_1P7B, "Qwen3-1.7B", 4096, (1, 8, 64)),
+          "32b": (QWEN3_32B, "Qwen3-32B", 8192, (1, 8, 32))}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE_SIZE = 64
@@ -156,16 +175,95 @@ def time_decode(runner, sampler, rids, vocab, steps, warmup, gen, clocks=None):
     return ms / steps, launches, (a, b)
 
 
+def serve_workload(engine, vocab, n_req=64, lo=128, hi=2048, n_out=256, seed=0):
+    """64 requests at once through Engine.add_request / Engine.step; the measures of the
+    reference's live loop (src/serve.ts:280-550): throughput, time to first token, time
+    between tokens."""
+    import torch
+    from binfer_b200.sampling import SamplingParams
+    gen = torch.Generator().manual_seed(seed)
+    lens = torch.randint(lo, hi + 1, (n_req,), generator=gen).tolist()
+    prompts = [torch.randint(0, vocab, (n,), generator=gen).tolist() for n in lens]
+    engine.warm_up()
+    engine.time_gpu, engine.gpu_spans, engine.step_ms = True, [], []
+    pre0 = engine.scheduler.num_preemptions
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rids = [engine.add_request(p, SamplingParams(max_tokens=n_out, ignore_eos=True, seed=i))
+            for i, p in enumerate(prompts)]
+    first, last, seen = {}, {}, {r: 0 for r in rids}
+    steps = 0
+    while engine.has_work():
+        arrived = engine.step()
+        now = time.perf_counter() - t0
+        steps += 1
+        for req in arrived:
+            n = len(req.output) - req.unresolved
+            if n > seen.get(req.rid, 0):
+                first.setdefault(req.rid, now)
+                last[req.rid] = now
+                seen[req.rid] = n
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    engine.time_gpu = False
+    gpu_ms = sum(a.elapsed_time(b) for a, b, _ in engine.gpu_spans)
+    outs = [engine.requests.pop(r) for r in rids]
+    n_out_total = sum(len(r.output) for r in outs)
+    itl = [(last[r] - first[r]) / (seen[r] - 1) for r in rids if seen[r] > 1]
+    return {
+        "requests": n_req, "prompt_tokens": sum(lens), "output_tokens": n_out_total,
+        "wall_s": wall, "output_tok_s": n_out_total / wall,
+        "total_tok_s": (sum(lens) + n_out_total) / wall,
+        "ttft_ms_mean": 1e3 * statistics.mean(first.values()),
+        "ttft_ms_max": 1e3 * max(first.values()),
+        "itl_ms_mean": 1e3 * statistics.mean(itl),
+        "preemptions": engine.scheduler.num_preemptions - pre0, "steps": steps,
+        "host_step_s": sum(engine.step_ms) / 1e3, "gpu_busy_s": gpu_ms / 1e3,
+        "gpu_idle_frac": max(0.0, 1.0 - gpu_ms / 1e3 / wall),
+    }
+
+
+def serve_point(peaks, layers=None, page_size=PAGE_SIZE):
+    """The continuous-batching workload on the Qwen3-1.7B shape, with the bound its decode
+    steps have (every weight once and the live cache at the copy bandwidth, batch 64)."""
+    import torch
+    from binfer_b200 import Engine, Qwen3Config
+    raw = dict(QWEN3_1P7B)
+    full = raw["num_hidden_layers"]
+    if layers:
+        raw["num_hidden_layers"] = layers
+    cfg = Qwen3Config.from_dict(raw)
+    engine = Engine(cfg, "bfloat16", random_seed=1, page_size=page_size, max_seq_len=4096,
+                    max_batch_size=64, max_tokens_per_step=2048,
+                    num_pages=64 * (4096 // page_size) + 64)
+    r = serve_workload(engine, cfg.vocab_size)
+    weight_bytes = engine.model.weight_bytes()
+    mean_ctx = r["prompt_tokens"] / r["requests"] + 128
+    step_s = (weight_bytes + 64 * mean_ctx * cfg.kv_bytes_per_token(2)) / (peaks["hbm_gbs"] * 1e9)
+    r["decode_bound_tok_s"] = 64 / step_s
+    r["layers"], r["layers_of_full_config"] = cfg.num_hidden_layers, full
+    engine.runner.check_errors()
+    del engine
+    torch.cuda.empty_cache()
+    return r
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
+                    help="layer sizes: the headline's Qwen3-8B, or the 1.7B / 32B shapes")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve"],
+                    help="serve: the continuous-batching workload on the Qwen3-1.7B shape")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE)
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (named in the record)")
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip the other batches, the "
+                    "16-token pages, the serve workload and the prefill")
     ap.add_argument("--decode-only", action="store_true",
                     help="only the device-timed decode steps (for profiling): no e2e, no points")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for profiling)")
@@ -176,26 +274,38 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    peaks = load_peaks()
+    if args.workload == "serve":
+        r = serve_point(peaks, args.layers, args.page_size)
+        print(json.dumps({"metric": "continuous batching, 64 requests x [128, 2048] prompt "
+                                    "tokens x 256 output tokens (Qwen3-1.7B shape, bf16, 1 B200)",
+                          "value": r["output_tok_s"], "unit": "output tokens/s", "n_gpus": 1,
+                          "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                          "impl": "ours", "serve": r}))
+        return 0
 
     import torch
     from binfer_b200 import Engine, Qwen3Config
     from binfer_b200.csrc import ops
+    from binfer_b200.engine import make_runner
     from binfer_b200.engine.runner import StepItem
 
-    peaks = load_peaks()
-    raw = dict(QWEN3_8B)
+    base, shape_name, context, batches = SHAPES[args.shape]
+    raw = dict(base)
     full_layers = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
     cfg = Qwen3Config.from_dict(raw)
-    steps, warmup, B = args.steps, args.warmup, args.batch
+    steps, warmup = args.steps, args.warmup
+    B = args.batch or batches[1]
+    page_size = args.page_size
     if args.decode_only:
         args.no_points = True
-    max_b = max(B, 1 if args.no_points else 64)
-    pages = max_b * (CONTEXT // PAGE_SIZE) + 64
+    max_b = max(B, 1 if args.no_points else max(batches))
+    pages = max_b * (context // page_size) + 64
     t0 = time.time()
-    engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=pages, page_size=PAGE_SIZE,
-                    max_seq_len=CONTEXT, max_batch_size=max_b, max_tokens_per_step=2048,
+    engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=pages, page_size=page_size,
+                    max_seq_len=context, max_batch_size=max_b, max_tokens_per_step=2048,
                     cuda_graphs=not args.eager)
     runner, sampler = engine.runner, engine.sampler
     vocab = cfg.vocab_size
@@ -209,26 +319,38 @@ def main():
     clocks = ClockSampler()
     clocks.start()
 
-    def decode_point(batch, n_steps, n_warm):
-        start_len = CONTEXT - (n_steps + n_warm)
-        rids = fill_cache(engine, runner, batch, start_len, vocab, gen)
-        ms, launches, span = time_decode(runner, sampler, rids, vocab, n_steps, n_warm, gen, clocks)
+    def decode_point(batch, n_steps, n_warm, run=None):
+        run = run or runner
+        start_len = context - (n_steps + n_warm)
+        rids = fill_cache(engine, run, batch, start_len, vocab, gen)
+        ms, launches, span = time_decode(run, sampler, rids, vocab, n_steps, n_warm, gen, clocks)
         mean_ctx = start_len + n_warm + n_steps / 2
         for r in rids:
-            runner.free_request(r)
+            run.free_request(r)
         return ms, launches, span, mean_ctx
 
-    # ---- the headline: batch B at context 4096
+    def hbm_frac(batch, ms, mean_ctx):
+        return (weight_bytes + batch * mean_ctx * kv_per_token) / (ms / 1e3) / 1e9 / peaks["hbm_gbs"]
+
+    # ---- the headline: batch B at the shape's context
     ms_step, launches, span, mean_ctx = decode_point(B, steps, warmup)
     value = B / (ms_step / 1e3)
     bytes_step = weight_bytes + B * mean_ctx * kv_per_token
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     clk = clocks.summary(*span)
+    if clk["samples"] < 3:
+        # a short timed region falls between two samples of the clock: time it once more,
+        # long enough for a few of them (these steps are not the reported ones)
+        extra = max(steps, int(600 / max(ms_step, 0.1)))
+        _, _, span2, _ = decode_point(B, min(extra, context // 4), warmup)
+        clk = clocks.summary(*span2)
+        clk["note"] = "sampled over a longer run of the same steps"
 
     if args.decode_only:
         clocks.stop()
         print(json.dumps({"decode_only": True, "ms_per_step": ms_step, "value": value,
-                          "layers": cfg.num_hidden_layers, "batch": B,
+                          "layers": cfg.num_hidden_layers, "batch": B, "shape": args.shape,
+                          "page_size": page_size,
                           "roofline_frac": achieved / peaks["hbm_gbs"], "clocks": clk}))
         return 0
 
@@ -240,7 +362,7 @@ def main():
     # they are given room enough that none finishes (and the batch does not shrink) while
     # the steps are timed
     slack = 2 * B + 8
-    prompts = [torch.randint(0, vocab, (CONTEXT - (steps + warmup) - slack,),
+    prompts = [torch.randint(0, vocab, (context - (steps + warmup) - slack,),
                              generator=gen).tolist() for _ in range(B)]
     from binfer_b200.sampling import SamplingParams
     for p in prompts:
@@ -265,11 +387,14 @@ def main():
     while engine.has_work():
         engine.step()
 
-    points, prefill = {}, None
+    points, fracs, prefill, serve = {}, {}, None, None
     if not args.no_points:
-        for b in (1, 64):
-            ms_b, _, _, _ = decode_point(b, min(steps, 32), warmup)
+        for b in batches:
+            if b == B:
+                continue
+            ms_b, _, _, ctx_b = decode_point(b, min(steps, 32), warmup)
             points[f"decode_b{b}"] = b / (ms_b / 1e3)
+            fracs[f"decode_b{b}"] = round(hbm_frac(b, ms_b, ctx_b), 4)
         # ---- prefill of 2,048 tokens in one step
         toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
         times = []
@@ -292,21 +417,38 @@ def main():
             + 2 * H * vocab
         prefill = {"value": T / (pf_ms / 1e3), "tokens": T, "ms": pf_ms,
                    "frac": flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+        if args.shape == "8b" and page_size != 16:
+            # ---- the reference's block size: the same model over a cache of 16-token pages
+            small = make_runner(engine.model, engine.env, page_size=16,
+                                num_pages=max(batches) * (context // 16) + 64,
+                                max_requests=max(batches))
+            small.enable_decode_graphs(max_batch=max(batches), max_seq_len=context)
+            for b in (B, max(batches)):
+                ms_b, _, _, ctx_b = decode_point(b, min(steps, 32), warmup, run=small)
+                points[f"decode_b{b}_page16"] = b / (ms_b / 1e3)
+                fracs[f"decode_b{b}_page16"] = round(hbm_frac(b, ms_b, ctx_b), 4)
+            small.check_errors()
+            del small
     runner.check_errors()
+    if not args.no_points and args.shape == "8b":
+        del engine, runner
+        torch.cuda.empty_cache()
+        serve = serve_point(peaks)
+        points["serve_1p7b_output_tok_s"] = serve["output_tok_s"]
 
     out = {
-        "metric": "decode tok/s @ batch 8, context 4096 (Qwen3-8B shape, bf16, 1 B200)",
+        "metric": f"decode tok/s @ batch {B}, context {context} ({shape_name} shape, bf16, 1 B200)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape, random weights", "layers": cfg.num_hidden_layers,
+            "model": f"{shape_name} shape, random weights", "layers": cfg.num_hidden_layers,
             "layers_of_full_config": full_layers, "hidden": cfg.hidden_size,
             "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
             "vocab": cfg.vocab_size, "tied": cfg.tie_word_embeddings, "global_batch": B,
-            "seq_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "1 GPU",
-            "cuda_graphs": not args.eager, "l2": "inputs larger than L2 (weights 15 GB per step)",
+            "seq_len": context, "page_size": page_size, "parallelism": "1 GPU",
+            "cuda_graphs": not args.eager, "l2": f"inputs larger than L2 (weights {weight_bytes / 1e9:.0f} GB per step)",
             "clocks_sampled": "during the device-timed steps",
             "peaks": peaks["source"],
         },
@@ -316,9 +458,12 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"]},
         "points": points,
+        "points_hbm_frac": fracs,
     }
     if prefill is not None:
         out["prefill"] = prefill
+    if serve is not None:
+        out["serve"] = serve
     print(json.dumps(out))
     return 0
 

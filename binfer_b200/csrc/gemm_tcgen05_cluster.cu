@@ -253,17 +253,26 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       }
     }
   } else if (warp == 1 || warp == 3) {
-    // Two issuing threads, K steps in turn, an accumulator each (summed by the epilogue in
-    // a fixed order): issuing a tcgen05.mma costs its thread about a hundred cycles whatever
-    // the product's size, and with one thread that, not HBM, bounded the narrow projections.
+    // Two issuing threads, an accumulator each (summed by the epilogue in a fixed order):
+    // issuing a tcgen05.mma costs its thread about a hundred cycles whatever the product's
+    // size, and with one thread that, not HBM, bounded the narrow projections.
+    // A ring slot belongs to one issuer for good (slot s to issuer s % 2), so that the thread
+    // waits for every fill of its slots in turn.  An mbarrier's phase is one bit: with the K
+    // steps dealt out in turn and an odd number of slots, a thread met only every second fill
+    // of a slot, always with the same parity, and its wait for fill u + 2 passed while fill
+    // u + 1 was still in flight whenever the copies of several later steps had overtaken it.
+    // The product then read a slot that was being written and freed it under the copy: rare
+    // with few K steps, an "unspecified launch failure" (or a wait that gave up) once in a
+    // thousand launches with a hundred of them.
     const int who = warp == 1 ? 0 : 1;
     if (lane == 0 && who < p.issuers && kc1 - kc0 > who) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                              ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(p.mma_rows >> 4) << 24);
       const uint32_t acc = tmem_base + (uint32_t)(who * p.acc_stride);
-      bool ok = true;
-      for (int n = who; n < kc1 - kc0; n += p.issuers) {
+      bool ok = true, first = true;
+      for (int n = 0; n < kc1 - kc0; ++n) {
         const int stage = n % STAGES;
+        if (p.issuers == 2 && (stage & 1) != who) continue;
         if (!mbar_wait(full + stage, (uint32_t)(n / STAGES) & 1u, abort)) {
           ok = false;
           break;
@@ -275,7 +284,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
           umma_bf16(acc, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                    (n > who || k > 0) ? 1u : 0u);
+                    (!first || k > 0) ? 1u : 0u);
+        first = false;
         umma_commit(empty + stage);
       }
       if (ok) umma_commit(acc_full);

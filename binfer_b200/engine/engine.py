@@ -82,6 +82,9 @@ class Engine:
         self.tokens_prefilled = 0
         self.tokens_decoded = 0
         self.step_ms: List[float] = []
+        # with time_gpu set, every step is bracketed by CUDA events: (start, end, tokens)
+        self.time_gpu = False
+        self.gpu_spans: List[tuple] = []
 
     # ---------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -183,6 +186,9 @@ class Engine:
                 src = prev_rows[id(s.request)]
             items.append(StepItem(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.sample else [],
                                   src_row=src))
+        if self.time_gpu:
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev0.record()
         logits = self.runner.step(items, device_ids=prev_ids)
         sampling = [s for s in plan if s.sample]
         handle = None
@@ -191,6 +197,10 @@ class Engine:
                 logits, [s.request.params for s in sampling],
                 [len(s.request.output) for s in sampling],
                 [s.request.output for s in sampling], extra=self.runner.err)
+        if self.time_gpu:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            self.gpu_spans.append((ev0, ev1, sum(len(s.tokens) for s in plan)))
         for s in plan:
             if len(s.tokens) > 1 or not s.request.output:
                 self.tokens_prefilled += len(s.tokens)

@@ -80,6 +80,11 @@ QWEN3_8B_TWO_LAYERS = dict(
     use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu",
     attention_bias=False)
 
+# the layer sizes of the Qwen3-1.7B shape (tied head), two layers of its 28
+QWEN3_1P7B_TWO_LAYERS = dict(
+    QWEN3_8B_TWO_LAYERS, hidden_size=2048, num_attention_heads=16, num_key_value_heads=8,
+    intermediate_size=6144, tie_word_embeddings=True)
+
 # for the smoke test: small, but of the sizes that a decode step's tcgen05 kernels take
 # (2048 inputs to every projection, heads of 128, a head product over more than 65536 words)
 SMOKE_WIDE = dict(

@@ -160,3 +160,44 @@ def test_look_ahead_gives_the_same_tokens(cuda_device, tmp_path, temperature):
     tight = _engine(d, page_size=8, num_pages=14, look_ahead=True)
     assert tight.generate(prompts, **kw) == want
     assert tight.stats()["preemptions"] > 0
+
+
+def test_continuous_batching_at_qwen3_1p7b_layer_sizes(cuda_device, tmp_path):
+    """The scheduler at real layer sizes (two layers of the Qwen3-1.7B shape): eight requests
+    with prompts of 128 to 512 tokens and 160 output tokens each, submitted at once, a step
+    budget of 512 tokens (so prompts come in portions beside decoding requests), and a pool
+    that holds all the prompts but not what they grow into, so that requests are preempted
+    and recomputed.  float32: the
+    tokens are those of a run with room to spare (every sum's order depends on the position
+    only).  bfloat16, same pool: tokens that the plain implementation also ranks first, up
+    to what bfloat16 rounding can tell apart."""
+    from binfer_b200 import Engine, Qwen3Config
+    from binfer_b200.weights import write_model_dir
+    cfg = Qwen3Config.from_dict(H.QWEN3_1P7B_TWO_LAYERS)
+    d = write_model_dir(cfg, str(tmp_path / "qwen3_1p7b_two_layers"), seed=17, std=0.02,
+                        norm_std=0.05, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(128, 513, (8,), generator=g).tolist()
+    prompts = [H.random_tokens(n, cfg.vocab_size, 1000 + n) for n in lens]
+    kw = dict(page_size=64, max_seq_len=1024, max_batch_size=8, max_tokens_per_step=512)
+    n_out = 160
+    need = sum(-(-(n + n_out) // 64) for n in lens)
+    few = sum(-(-n // 64) for n in lens) + 10        # the prompts, a page each to grow into
+    roomy = Engine(d, "float32", num_pages=need + 8, **kw)
+    want = roomy.generate(prompts, max_tokens=n_out, ignore_eos=True)
+    assert roomy.stats()["preemptions"] == 0
+    del roomy
+    tight = Engine(d, "float32", num_pages=few, **kw)
+    got = tight.generate(prompts, max_tokens=n_out, ignore_eos=True)
+    assert tight.stats()["preemptions"] > 0
+    assert got == want
+    assert tight.stats()["pages_free"] == tight.stats()["pages_total"]
+    del tight
+    torch.cuda.empty_cache()
+    eng = Engine(d, "bfloat16", num_pages=few, **kw)
+    out = eng.generate(prompts, max_tokens=n_out, ignore_eos=True)
+    assert eng.stats()["preemptions"] > 0 and all(len(o) == n_out for o in out)
+    assert eng.runner.graph_replays > 0
+    raw, w = H.read_model_dir(d)
+    w = {k: t.to(torch.float64) for k, t in w.items()}
+    H.assert_greedy_within_rounding(raw, w, prompts[:3], out[:3])

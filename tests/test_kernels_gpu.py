@@ -672,3 +672,26 @@ def test_gemm_bf16_cluster_split_k(cuda_device, M, N, K, bn, c, out_dtype):
     assert not ops.gemm_bf16_cluster(torch.zeros(65, K, device=cuda_device, dtype=BF16), w,
                                      torch.empty(65, N, device=cuda_device, dtype=out_dtype),
                                      err, bn, c)
+
+
+@pytest.mark.parametrize("N,K,bn,c", [(5120, 25600, 192, 4), (5120, 8192, 192, 4)])
+def test_gemm_bf16_cluster_many_k_steps_many_launches(cuda_device, N, K, bn, c):
+    """A hundred K steps per CTA through a ring of seven slots, two issuing threads, a
+    thousand launches: every launch gives the first one's bits and no wait gives up.  (Each
+    ring slot has one issuer: were the K steps dealt out in turn, a thread would wait for
+    every second fill of a slot with the same parity, which held only while the copies
+    landed in order.  The Qwen3-32B shape's output and down projections are these sizes.)"""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(8, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(BF16).to(cuda_device)
+    err = ops.error_word(cuda_device)
+    first = torch.empty((8, N), device=cuda_device, dtype=BF16)
+    assert ops.gemm_bf16_cluster(x, w, first, err, bn, c)
+    _close(first, x.double().cpu() @ w.double().cpu().T, BF16)
+    out = torch.empty_like(first)
+    same = torch.ones((), dtype=torch.bool, device=cuda_device)
+    for _ in range(1000):
+        assert ops.gemm_bf16_cluster(x, w, out, err, bn, c)
+        same &= (out == first).all()
+    assert bool(same) and int(err.item()) == 0
