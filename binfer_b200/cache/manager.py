@@ -109,7 +109,8 @@ class CacheGroup:
         self.index = index
         self.need = need
         self.page_size = page_size
-        self.pool = PagePool(num_pages)
+        # pages of one 128-key attention tile lie side by side in the pool where they can
+        self.pool = PagePool(num_pages, run=max(1, 128 // page_size))
         self.entries: List[int] = []           # schedule entries stored here, in order
         self.storage = None                    # device tensor, see allocate_storage()
 
@@ -225,7 +226,8 @@ class CacheManager:
             self._release_passed(g, rc, table)
             want = -(-new_len // g.page_size)
             while len(table) < want:
-                table.append(g.pool.alloc())
+                table.append(g.pool.alloc(after=max(table[-1], 0) if table else 0,
+                                          index=len(table)))
 
     def _release_passed(self, g: CacheGroup, rc: RequestCache, table: List[int]) -> None:
         first = min(g.first_needed_page(rc.length), len(table))

@@ -137,6 +137,8 @@ template <int D>
 __global__ void __launch_bounds__(DP_THREADS, 1)
 decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
                                    const __grid_constant__ CUtensorMap map_v,
+                                   const __grid_constant__ CUtensorMap map_k_run,
+                                   const __grid_constant__ CUtensorMap map_v_run,
                                    const __nv_bfloat16* __restrict__ q,
                                    const int* __restrict__ rows,
                                    const int* __restrict__ seq_of_token,
@@ -269,6 +271,12 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
         const int r = __shfl_sync(0xffffffffu, cur.r, src);
         const int g = __shfl_sync(0xffffffffu, cur.g, src);
         const int split = __shfl_sync(0xffffffffu, cur.split, src);
+        // the tile's pages lie side by side in the pool (what a prompt's pages do, and a
+        // decoding request's where the pool could give it neighbours): one box for all of them
+        const int y0 = __shfl_sync(0xffffffffu, y, 0);
+        const bool run = pages > 1 && __all_sync(0xffffffffu, lane >= pages ||
+                                                 y == y0 + lane * nkv * page_size);
+        const int page0 = y0 / (nkv * page_size);
         const int pgrp = it % groups, k = it / groups;
         const int qi = pgrp * qsg + k % qsg;
         bool ok = true;
@@ -295,7 +303,11 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
             }
           }
           __syncwarp();
-          if (lane < pages) {
+          if (run) {
+            if (lane < HALVES)
+              bf_tma_load_4d(tiles + (size_t)slot * TILE_ELEMS + lane * HALF_ELEMS, &map_k_run,
+                             full + slot, lane * 64, 0, g, page0);
+          } else if (lane < pages) {
             __nv_bfloat16* dst = tiles + (size_t)slot * TILE_ELEMS + lane * page_size * 64;
 #pragma unroll
             for (int hh = 0; hh < HALVES; ++hh)
@@ -311,7 +323,11 @@ decode_attention_persistent_kernel(const __grid_constant__ CUtensorMap map_k,
           }
           if (lane == 0) bf_mbar_expect_tx(full + slot, TILE_BYTES);
           __syncwarp();
-          if (lane < pages) {
+          if (run) {
+            if (lane < HALVES)
+              bf_tma_load_4d(tiles + (size_t)slot * TILE_ELEMS + lane * HALF_ELEMS, &map_v_run,
+                             full + slot, lane * 64, 0, g, page0);
+          } else if (lane < pages) {
             __nv_bfloat16* dst = tiles + (size_t)slot * TILE_ELEMS + lane * page_size * 64;
 #pragma unroll
             for (int hh = 0; hh < HALVES; ++hh)
@@ -520,6 +536,14 @@ static int launch_persistent(const void* q, const void* k_cache, const void* v_c
   if (e) return e;
   e = bf_make_tensor_map_bf16_2d(&mv, v_cache, cache_rows, D, D, page_size, 64);
   if (e) return e;
+  // the same pages as a 4-d tensor, for tiles whose pages are neighbours in the pool
+  CUtensorMap mkr, mvr;
+  e = bf_make_tensor_map_pages_bf16(&mkr, k_cache, num_pages, nkv, page_size, D,
+                                    DP_SPLIT / page_size);
+  if (e) return e;
+  e = bf_make_tensor_map_pages_bf16(&mvr, v_cache, num_pages, nkv, page_size, D,
+                                    DP_SPLIT / page_size);
+  if (e) return e;
   auto kern = decode_attention_persistent_kernel<D>;
   static bool configured_on[BF_MAX_DEVICES];
   bool& configured = configured_on[bf_current_device()];
@@ -533,7 +557,7 @@ static int launch_persistent(const void* q, const void* k_cache, const void* v_c
   if (sms <= 0) return (int)cudaErrorInvalidValue;
   const long long most = (long long)n_rows * nkv * max_splits;
   const int grid = (int)(most < sms ? most : sms);
-  return bf_launch_pdl(kern, dim3(grid), dim3(DP_THREADS), smem, stream, mk, mv,
+  return bf_launch_pdl(kern, dim3(grid), dim3(DP_THREADS), smem, stream, mk, mv, mkr, mvr,
                        (const __nv_bfloat16*)q, rows, seq_of_token, positions, block_tables,
                        table_stride, part_o, part_ml, n_rows, nh, nkv, page_size, num_pages,
                        window, max_splits, scale * 1.4426950408889634f, slots, groups,

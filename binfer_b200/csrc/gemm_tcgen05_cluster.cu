@@ -575,9 +575,13 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   int stages = (int)((smem_max - fixed) / stage_bytes);
   if (stages > CL_MAX_STAGES) stages = CL_MAX_STAGES;
   if (stages < 2) return (int)cudaErrorInvalidValue;
-  p.stages = stages;
   static const int issuers = getenv("BINFER_B200_GEMM_ISSUERS") ? atoi(getenv("BINFER_B200_GEMM_ISSUERS")) : 2;
   p.issuers = issuers == 1 ? 1 : 2;
+  // an even ring with two issuers: slot s belongs to issuer s % 2, so the K steps go to the
+  // issuers strictly in turn
+  static const int even = getenv("BINFER_B200_GEMM_EVEN_STAGES") ? atoi(getenv("BINFER_B200_GEMM_EVEN_STAGES")) : 1;
+  if (even && p.issuers == 2) stages -= stages % 2;
+  p.stages = stages;
   // With at most 32 token rows (a 64-row product keeps rows 0..15 in tensor memory lanes
   // 0..15 and rows 16..31 in lanes 32..47) a 64-row product does: half the tensor work per
   // weight byte.  The time of one product is

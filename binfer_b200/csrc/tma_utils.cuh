@@ -42,6 +42,29 @@ static inline int bf_make_tensor_map_bf16_2d(CUtensorMap* map, const void* base,
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// The paged cache [pages, heads, page_size, d] (bf16) as a 4-d tensor, fetched in boxes of
+// `box_pages` whole pages of one head and 64 columns: {64, page_size, 1, box_pages}.  In
+// shared memory the box is box_pages * page_size rows of 128 bytes, page after page, in the
+// 128-byte swizzle: what box_pages separate boxes of the 2-d view above would leave, one
+// behind the other (page_size is a multiple of 8, the swizzle's period in rows).  For pages
+// that lie side by side in the pool: one instruction instead of one per page.
+static inline int bf_make_tensor_map_pages_bf16(CUtensorMap* map, const void* base,
+                                                long long pages, int heads, int page_size, int d,
+                                                int box_pages) {
+  BfEncodeTiledFn enc = bf_encode_tiled();
+  if (!enc) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)heads,
+                              (cuuint64_t)pages};
+  const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)page_size * d * 2,
+                                 (cuuint64_t)heads * page_size * d * 2};
+  const cuuint32_t box[4] = {64u, (cuuint32_t)page_size, 1u, (cuuint32_t)box_pages};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t bf_smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -79,6 +102,15 @@ __device__ __forceinline__ void bf_tma_load_2d(void* smem_dst, const CUtensorMap
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4}], [%2];" ::"r"(bf_smem_u32(smem_dst)),
       "l"(map), "r"(bf_smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// (x: column, a multiple of 8 elements = 16 bytes; the other coordinates have no rule)
+__device__ __forceinline__ void bf_tma_load_4d(void* smem_dst, const CUtensorMap* map,
+                                               uint64_t* bar, int x, int row, int head, int page) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(bf_smem_u32(smem_dst)),
+      "l"(map), "r"(bf_smem_u32(bar)), "r"(x), "r"(row), "r"(head), "r"(page)
       : "memory");
 }
 #endif

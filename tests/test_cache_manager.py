@@ -188,3 +188,54 @@ def test_a_windowed_request_runs_through_a_small_pool():
         cm.check_consistent()
     cm.free_request("r")
     assert cm.groups[0].pool.num_held == 0
+
+
+def test_pages_of_a_tile_are_neighbours_where_the_pool_allows():
+    """Two requests that grow in turn, a page at a time: with 16-token pages a 128-key tile
+    is eight pages, and each request's eight lie side by side in the pool, because a request
+    starts a tile in a run of pages that is wholly free and then takes the page behind its
+    last one.  When no such page is left, it takes any: nothing is ever refused."""
+    cm = CacheManager([KVNeed(1, 8)], page_size=16, num_pages=40, max_requests=4)
+    for rid in "ab":
+        cm.add_request(rid)
+    for n in range(1, 17):                     # 16 pages each, in turn
+        for rid in "ab":
+            cm.reserve(rid, 16 * n)
+            cm.commit(rid, 16 * n)
+    for rid in "ab":
+        t = cm.get(rid).tables[0]
+        for tile in (t[:8], t[8:]):
+            assert tile == list(range(tile[0], tile[0] + 8)), (rid, t)
+    cm.check_consistent()
+    # 8 pages are left, one whole run: c takes it, d finds only scattered pages later
+    cm.add_request("c")
+    cm.reserve("c", 16 * 8)
+    assert cm.num_free_pages() == [0]
+    cm.free_request("a")
+    cm.add_request("d")
+    cm.reserve("d", 16 * 16)                   # a's pages, whatever their order
+    assert cm.num_free_pages() == [0]
+    cm.check_consistent()
+    for rid in "bcd":
+        cm.free_request(rid)
+    assert cm.groups[0].pool.num_held == 0
+
+
+def test_page_pool_with_runs_never_loses_a_page():
+    import random
+    from binfer_b200.cache.pages import PagePool
+    rng = random.Random(5)
+    pool = PagePool(37, run=8)
+    held = []
+    for _ in range(20000):
+        if held and (rng.random() < 0.5 or pool.num_free == 0):
+            pool.free(held.pop(rng.randrange(len(held))))
+        else:
+            after = rng.choice(held) if held and rng.random() < 0.7 else 0
+            p = pool.alloc(after=after, index=rng.randrange(20))
+            assert p not in held and 1 <= p <= 37
+            held.append(p)
+        assert pool.num_free == 37 - len(held)
+    while pool.num_free:                        # every free page can still be had
+        held.append(pool.alloc())
+    assert sorted(held) == list(range(1, 38))

@@ -136,14 +136,17 @@ def test_qk_norm_rope_kv_write(cuda_device, dtype, nh, nkv, d, rot, norm):
 
 
 # ----------------------------------------------------------------------- attention
-def _paged(k, v, ps, dev, dtype, seed=0):
-    """Scatter dense k, v ``[n, nkv, d]`` of one request into shuffled pages.
+def _paged(k, v, ps, dev, dtype, seed=0, neighbours=False):
+    """Scatter dense k, v ``[n, nkv, d]`` of one request into shuffled pages (or, with
+    ``neighbours``, into pages that lie side by side in the pool).
     Returns caches ``[pages, nkv, ps, d]`` and the block table."""
     n, nkv, d = k.shape
     n_pages = -(-n // ps)
     total = n_pages + 5
     g = torch.Generator().manual_seed(seed)
     ids = (torch.randperm(total - 1, generator=g)[:n_pages] + 1).tolist()   # page 0 unused
+    if neighbours:
+        ids = list(range(3, 3 + n_pages))
     kc = torch.randn(total, nkv, ps, d, generator=g).to(dtype)              # junk elsewhere
     vc = torch.randn(total, nkv, ps, d, generator=g).to(dtype)
     for j in range(n):
@@ -152,7 +155,8 @@ def _paged(k, v, ps, dev, dtype, seed=0):
     return kc.to(dev), vc.to(dev), ids
 
 
-def _attention_case(dev, dtype, nh, nkv, d, ps, ctxs, qlens, window, spike=False, seed=0):
+def _attention_case(dev, dtype, nh, nkv, d, ps, ctxs, qlens, window, spike=False, seed=0,
+                    neighbours=False):
     """Requests with contexts ``ctxs``, the last ``qlens`` tokens of each being queries."""
     g = torch.Generator().manual_seed(seed)
     ks, vs, qs, tables, refs = [], [], [], [], []
@@ -176,7 +180,7 @@ def _attention_case(dev, dtype, nh, nkv, d, ps, ctxs, qlens, window, spike=False
                 k[far - 1, :, 0] = 64.0
                 v[far - 1] = -7.0
         ref = P.causal_attention(q, k, v, d ** -0.5, window)[n - ql:]
-        kc, vc, ids = _paged(k, v, ps, "cpu", dtype, seed + b)
+        kc, vc, ids = _paged(k, v, ps, "cpu", dtype, seed + b, neighbours)
         kcs.append(kc)
         vcs.append(vc)
         tables.append([i + page_base for i in ids])
@@ -241,6 +245,31 @@ def test_decode_attention_split_kv(cuda_device, nh, nkv, d, ps, window, spike, v
     for r in (5, 2, 4):
         assert torch.equal(out2[r], out[r])
     assert float(out2[0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [
+    (8, 2, 128, 16, None), (32, 8, 128, 16, 300), (6, 3, 64, 8, None), (4, 4, 256, 32, None),
+    (8, 4, 128, 64, 1000)])
+def test_decode_attention_with_pages_side_by_side(cuda_device, nh, nkv, d, ps, window):
+    """Tiles whose pages are neighbours in the pool arrive as one box: the same bits as with
+    the pages scattered (one box a page), and the plain result.  Contexts that end inside a
+    tile, rows shorter than a tile, a window that starts inside one."""
+    from binfer_b200.csrc import ops
+    ctxs = [1, 127, 128, 129, 300, 1000, 45, 2050, 640]
+    qlens = [1] * len(ctxs)
+    outs = []
+    for neighbours in (True, False):
+        q, kc, vc, sot, pos, bt, ref = _attention_case(
+            cuda_device, BF16, nh, nkv, d, ps, ctxs, qlens, window, True, seed=13,
+            neighbours=neighbours)
+        out = torch.zeros_like(q)
+        err = _err(cuda_device)
+        ops.decode_attention(q, kc, vc, None, len(ctxs), sot, pos, bt, out, nh, nkv, d, window,
+                             d ** -0.5, max(ctxs), err, variant="persistent")
+        assert int(err.item()) == 0
+        _close(out, ref, BF16)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]), "the result depends on where the pages lie"
 
 
 @pytest.mark.parametrize("nh,nkv,d,ps,window", [
