@@ -20,8 +20,8 @@ is one decode step (one new token per request).  One JSON line is printed with
 - ``roofline``: bytes the decode step must read (every weight once, the cache of
   the live requests) over its time, against the measured copy bandwidth;
 - ``points``: decode tokens per second at batch 1 and 64, at batch 8 and 64 with
-  16-token pages (the reference's block size; the engine's default page is 64 tokens), and
-  the output tokens per second of the continuous-batching workload below;
+  64-token pages (the run itself has the reference's block size, 16 tokens), and the
+  output tokens per second of the continuous-batching workload below;
 - ``clocks``: SM clock and throttle reasons sampled during the timed region.
 
 Between timed steps the inputs (15 GB of weights, gigabytes of cache) are far
@@ -62,7 +62,7 @@ SHAPES = {"8b": (QWEN3_8B, "Qwen3-8B", 4096, (1, 8, 64)),
           "32b": (QWEN3_32B, "Qwen3-32B", 8192, (1, 8, 32))}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
-PAGE_SIZE = 64
+PAGE_SIZE = 16          # the reference's block size, and the configuration's
 
 
 def load_peaks():
@@ -392,7 +392,7 @@ def main():
         for b in batches:
             if b == B:
                 continue
-            ms_b, _, _, ctx_b = decode_point(b, min(steps, 32), warmup)
+            ms_b, _, _, ctx_b = decode_point(b, steps, warmup)
             points[f"decode_b{b}"] = b / (ms_b / 1e3)
             fracs[f"decode_b{b}"] = round(hbm_frac(b, ms_b, ctx_b), 4)
         # ---- prefill of 2,048 tokens in one step
@@ -417,18 +417,19 @@ def main():
             + 2 * H * vocab
         prefill = {"value": T / (pf_ms / 1e3), "tokens": T, "ms": pf_ms,
                    "frac": flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
-        if args.shape == "8b" and page_size != 16:
-            # ---- the reference's block size: the same model over a cache of 16-token pages
-            small = make_runner(engine.model, engine.env, page_size=16,
-                                num_pages=max(batches) * (context // 16) + 64,
-                                max_requests=max(batches))
-            small.enable_decode_graphs(max_batch=max(batches), max_seq_len=context)
+        if args.shape == "8b":
+            # ---- the same model over a cache of the other page size (64 tokens, or 16)
+            other = 64 if page_size != 64 else 16
+            second = make_runner(engine.model, engine.env, page_size=other,
+                                 num_pages=max(batches) * (context // other) + 64,
+                                 max_requests=max(batches))
+            second.enable_decode_graphs(max_batch=max(batches), max_seq_len=context)
             for b in (B, max(batches)):
-                ms_b, _, _, ctx_b = decode_point(b, min(steps, 32), warmup, run=small)
-                points[f"decode_b{b}_page16"] = b / (ms_b / 1e3)
-                fracs[f"decode_b{b}_page16"] = round(hbm_frac(b, ms_b, ctx_b), 4)
-            small.check_errors()
-            del small
+                ms_b, _, _, ctx_b = decode_point(b, steps, warmup, run=second)
+                points[f"decode_b{b}_page{other}"] = b / (ms_b / 1e3)
+                fracs[f"decode_b{b}_page{other}"] = round(hbm_frac(b, ms_b, ctx_b), 4)
+            second.check_errors()
+            del second
     runner.check_errors()
     if not args.no_points and args.shape == "8b":
         del engine, runner

@@ -66,7 +66,7 @@ Options:
   --kv-memory-gb <f>       Memory for the key/value cache (default: 0.9 of what is free
                            after loading, at most max-batch-size x max-seq-len tokens)
   --kv-pages <n>           Size of the cache in pages instead
-  --page-size <n>          Tokens per cache page (default: 64)
+  --page-size <n>          Tokens per cache page (default: 16)
   --max-tokens-per-step <n>  Token budget of one step (default: 2048)
   --max-seq-len <n>        Longest sequence (default: 4096)
   --max-batch-size <n>     Most requests running at once (default: 64)
@@ -114,7 +114,7 @@ def parse_args(argv: List[str]) -> dict:
              bench=False, profile=False, trace=None, quiet=False, verbose=False, cuda_graphs=True,
              temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=None,
              ignore_eos=False, input=None, output=None, use_template=False, random_weights=None,
-             kv_memory_gb=None, kv_pages=None, allow_unexpected_tensors=False, page_size=64, max_tokens_per_step=2048,
+             kv_memory_gb=None, kv_pages=None, allow_unexpected_tensors=False, page_size=16, max_tokens_per_step=2048,
              max_seq_len=4096, max_batch_size=64)
     names = {"--max-tokens": ("max_tokens", int), "--tp": ("tp", str), "--dtype": ("dtype", str),
              "-p": ("prompt", str), "--prompt": ("prompt", str), "--prompt-ids": ("prompt", str),

@@ -164,8 +164,10 @@ __device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f +
 // code: with all four behind run-time tests the plain product was 3 % slower.
 enum { FORM_PLAIN = 0, FORM_ADD_NORM = 1, FORM_QKV = 2, FORM_SWIGLU = 3 };
 
+constexpr int CL_THREADS = 256;       // eight warps: the roles of warps 1 to 3, then the epilogue
+
 template <typename OutT, int FORM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(CL_THREADS, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                     const ClusterGemmParams p) {
@@ -290,22 +292,26 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       }
       if (ok) umma_commit(acc_full);
     }
-  } else if (warp == 0 || warp == 4 || (warp == 5 && p.tok_rows > (p.mma_rows == 64 ? 16 : 32))) {
-    // Warps 0 and 4 may both read TMEM lanes 0..31 and share the tile's columns; warp 5 reads
-    // lanes 32..63.  A lane holds one token's row of the partial sum: row = lane for a
-    // 128-row product; a 64-row product keeps rows 16 q .. 16 q + 15 in the first 16 lanes of
-    // lane quarter q, so rows 16..31 are warp 5's.
-    const bool narrow = p.mma_rows == 64;
-    const int per = narrow ? 16 : 32;                      // rows a lane quarter holds
-    const int row = lane < per ? (warp == 5 ? per : 0) + lane : 1 << 20;
-    const uint32_t lanes = (uint32_t)(warp == 5 ? 32 : 0) << 16;
+  }
+  __syncwarp();
+  // The epilogue: every warp whose lane quarter holds token rows.  Warp w may read the tensor
+  // memory lanes of quarter w % 4 only; the two warps of a quarter (w and w + 4) share the
+  // tile's columns.  A lane holds one token's row of the partial sum: row = lane for a 128-row
+  // product; a 64-row product keeps rows 16 q .. 16 q + 15 in the first 16 lanes of quarter q
+  // (so 64 token rows use all four quarters, 16 of them only warps 0 and 4).  Warps 1 to 3
+  // come here when the last load or product is issued.
+  const int quarter = warp & 3;
+  const int per = p.mma_rows == 64 ? 16 : 32;            // rows a lane quarter holds
+  if (quarter * per < p.tok_rows) {
+    const int row = lane < per ? quarter * per + lane : 1 << 20;
+    const uint32_t lanes = (uint32_t)(quarter * 32) << 16;
     const int width = kAct ? p.bn / 2 : p.bn;          // columns to walk: outputs or sums
     const int chunks = (width + 15) / 16, half = (chunks + 1) / 2;
-    const int c_begin = warp == 4 ? half * 16 : 0, c_end = warp == 0 ? half * 16 : chunks * 16;
+    const int c_begin = warp >= 4 ? half * 16 : 0, c_end = warp < 4 ? half * 16 : chunks * 16;
     // (SwiGLU form) the factor of this lane's row, worked out while the products run
     float factor = 1.f;
     if (kAct && p.rs.partials)
-      for (int t = (warp == 5 ? per : 0); t < p.tokens && t < (warp == 5 ? 2 * per : per); ++t) {
+      for (int t = quarter * per; t < p.tokens && t < (quarter + 1) * per; ++t) {
         const float ft = bf_row_factor(p.rs, t, lane);
         if (t == row) factor = ft;
       }
@@ -431,15 +437,16 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   const int heads_per_tile = kQkv ? p.bn / p.d : 1;
   const int n_mine = kQkv && p.tokens > rank ? (p.tokens - rank + p.cluster - 1) / p.cluster : 0;
   const int turn = warp == 2 ? 0 : warp == 5 ? 1 : warp == 1 ? 2 : warp == 3 ? 3 : warp == 4 ? 4 : 5;
+  const bool takes_turns = kQkv && warp < 6;             // (six warps walk the tokens)
   QkvToken tk;
-  if (kQkv && turn < n_mine) tk = qkv_token(p, turn * p.cluster + rank, lane);
+  if (takes_turns && turn < n_mine) tk = qkv_token(p, turn * p.cluster + rank, lane);
 
   // every thread of every CTA of the cluster: partials are in place after this
   BF_TRACE_POINT(10 * BF_TR_GEMM + 3);
   cluster_sync_all();
   BF_TRACE_POINT(10 * BF_TR_GEMM + 4);
 
-  for (int it = turn * heads_per_tile; kQkv && it < n_mine * heads_per_tile; ++it) {
+  for (int it = turn * heads_per_tile; takes_turns && it < n_mine * heads_per_tile; ++it) {
     const int lt = it / heads_per_tile, hh = it - lt * heads_per_tile;
     if (hh == heads_per_tile - 1) it += 5 * heads_per_tile;      // on to the token 6 further
     const int t = lt * p.cluster + rank;
@@ -589,7 +596,7 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   // 128-row products for 8 tokens the SM clock settled near 1750 MHz instead of 1965 (36
   // layers, batch 8: 4.28 against 4.12 ms a step with every projection on this kernel).
   static const int rows = getenv("BINFER_B200_GEMM_MMA_ROWS") ? atoi(getenv("BINFER_B200_GEMM_MMA_ROWS")) : 64;
-  p.mma_rows = rows == 64 && p.tok_rows <= 32 ? 64 : 128;
+  p.mma_rows = rows == 64 ? 64 : 128;
   int need = p.issuers * p.bn, cols = 32;
   while (cols < need) cols *= 2;
   p.tmem_cols = cols;
@@ -612,7 +619,7 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   const int tiles = (p.features + p.bn - 1) / p.bn;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * p.cluster, 1, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(CL_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -750,7 +757,7 @@ static int resident_clusters(int c) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(c * 148, 1, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(CL_THREADS, 1, 1);
   cfg.dynamicSmemBytes = 200 * 1024;              // one CTA an SM, as every launch of it has
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -31,7 +31,7 @@ class Engine:
                  random_seed: Optional[int] = None, random_std: float = 0.02,
                  max_kv_memory_gb: Optional[float] = None, num_pages: Optional[int] = None,
                  gpu_memory_utilization: float = 0.9,
-                 page_size: int = 64, max_seq_len: int = 4096, max_batch_size: int = 64,
+                 page_size: int = 16, max_seq_len: int = 4096, max_batch_size: int = 64,
                  max_tokens_per_step: int = 2048, cuda_graphs: bool = True,
                  look_ahead: bool = True, device: str = "cuda:0",
                  allow_unexpected_tensors: bool = False):

@@ -70,7 +70,7 @@ def model_from_seed(config, env: BuildEnv, seed: int = 0, std: float = 0.02,
     return build_model(spec, env, source)
 
 
-def make_runner(model: DecoderModel, env: BuildEnv, page_size: int = 64,
+def make_runner(model: DecoderModel, env: BuildEnv, page_size: int = 16,
                 num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
                 max_requests: int = 64) -> ModelRunner:
     """A runner whose page pool holds ``num_pages`` pages per cache group, or enough

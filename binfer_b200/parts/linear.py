@@ -59,11 +59,16 @@ def _use_cluster(M: int, N: int, K: int) -> bool:
 _CLUSTER_MAX_FEATURES = int(os.environ.get("BINFER_B200_CLUSTER_MAX_FEATURES", "8192"))
 
 
+# most token rows that go to the cluster kernel under "auto"
+_CLUSTER_MAX_TOKENS = int(os.environ.get("BINFER_B200_CLUSTER_MAX_TOKENS", "64"))
+
+
 def cluster_token_limit() -> int:
     """Most token rows for which the policy sends products to the split-K cluster kernel."""
     if _POLICY == "library":
         return 0
-    return 32 if _POLICY == "auto" else ops.CLUSTER_MAX_TOKENS
+    return min(_CLUSTER_MAX_TOKENS, ops.CLUSTER_MAX_TOKENS) if _POLICY == "auto" \
+        else ops.CLUSTER_MAX_TOKENS
 
 
 _plans = {}
