@@ -650,8 +650,10 @@ BF_EXPORT int bf_gemm_cluster_plan(int features, int K, int num_sms, int* bn_out
   const int kc = (K + BK - 1) / BK;
   int best_ctas = 0, best_bn = 0, best_c = 0;
   const int order[3] = {4, 2, 1};
+  static const int max_c = getenv("BINFER_B200_CLUSTER_MAX_C") ? atoi(getenv("BINFER_B200_CLUSTER_MAX_C")) : 4;
   for (int i = 0; i < 3; ++i) {
     const int c = order[i];
+    if (c > max_c) continue;
     if (kc / c < 4) continue;
     const int max_ctas = (num_sms / c) * c;
     for (int bn = 256; bn >= 64; bn -= 16) {

@@ -88,15 +88,24 @@ def report(name, us, nbytes=None, flops=None, **extra):
     print(json.dumps(out), flush=True)
 
 
-def _paged_cache(dev, n_req, ctx, nkv, d, ps, sets):
-    """Random caches for n_req requests of ctx tokens, pages handed out in shuffled order."""
+def _paged_cache(dev, n_req, ctx, nkv, d, ps, sets, scattered=False):
+    """Random caches for n_req requests of ctx tokens.  Pages: the eight (128 / ps) of each
+    128-key tile side by side in the pool, the tiles themselves in shuffled order, as the
+    page pool hands them out; with ``scattered`` every page anywhere."""
     pages_per = -(-ctx // ps)
+    run = max(1, 128 // ps)
+    pages_per = -(-pages_per // run) * run
     total = n_req * pages_per + 1
     out = []
     for s in range(sets):
         kc = torch.randn(total, nkv, ps, d, device=dev, dtype=BF16)
         vc = torch.randn(total, nkv, ps, d, device=dev, dtype=BF16)
-        perm = (torch.randperm(total - 1, device=dev) + 1).to(torch.int32)
+        if scattered:
+            perm = (torch.randperm(total - 1, device=dev) + 1).to(torch.int32)
+        else:
+            runs = torch.randperm((total - 1) // run, device=dev).to(torch.int32)
+            perm = (runs[:, None] * run + 1 + torch.arange(run, device=dev, dtype=torch.int32)
+                    ).reshape(-1)
         bt = perm[: n_req * pages_per].view(n_req, pages_per).contiguous()
         out.append((kc, vc, bt))
     return out
@@ -107,7 +116,7 @@ def decode_attention(a):
     B, ctx, nh, nkv, d, ps = a.batch, a.ctx, a.heads, a.kv_heads, a.head_dim, a.page_size
     per_set = 2 * B * ctx * nkv * d * 2
     sets = max(2, int(3e8 // per_set) + 1)
-    caches = _paged_cache(dev, B, ctx, nkv, d, ps, sets)
+    caches = _paged_cache(dev, B, ctx, nkv, d, ps, sets, a.scattered)
     q = torch.randn(B, nh * d, device=dev, dtype=BF16)
     out = torch.empty_like(q)
     sot = torch.arange(B, dtype=torch.int32, device=dev)
@@ -281,7 +290,9 @@ def main(argv=None):
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
-    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--scattered", action="store_true",
+                    help="decode_attention: no two pages of a tile side by side in the pool")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=6, help="step_timeline: layers of the model")
     ap.add_argument("--intermediate", type=int, default=12288)

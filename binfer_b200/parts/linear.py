@@ -44,9 +44,7 @@ def _use_own(M: int, N: int, K: int) -> bool:
 
 
 def _use_cluster(M: int, N: int, K: int) -> bool:
-    # the kernel takes up to 64 tokens, but beyond 32 (where its products have 128 rows
-    # instead of 64) the library is faster inside a step: all 36 layers, 6.14 against 5.98 ms
-    # at 24 tokens, 6.96 against 6.97 at 32, 10.20 against 10.89 at 64 (library against own)
+    # (at 24 tokens the library takes 6.14 against the kernel's 5.98 ms, at 32: 6.96 against 6.97)
     if _POLICY == "library" or M > cluster_token_limit():
         return False
     # wider weights (the gate/up projection, on "clusters" of one CTA) measured 2 us slower
@@ -59,8 +57,14 @@ def _use_cluster(M: int, N: int, K: int) -> bool:
 _CLUSTER_MAX_FEATURES = int(os.environ.get("BINFER_B200_CLUSTER_MAX_FEATURES", "8192"))
 
 
-# most token rows that go to the cluster kernel under "auto"
-_CLUSTER_MAX_TOKENS = int(os.environ.get("BINFER_B200_CLUSTER_MAX_TOKENS", "64"))
+# most token rows that go to the cluster kernel under "auto".  The kernel takes 64 (64-row
+# products with all four lane quarters of tensor memory in use), but from 33 rows on the
+# library is faster inside a step, all 36 layers, 16-token pages: 7.31 against 7.45 ms at 33
+# tokens, 8.97 against 9.31 at 48, 10.87 against 11.39 at 64 (library against own; clusters
+# of 2 or 1 instead of 4: 11.71 and 13.85).  With 64 token rows a ring slot is 24 KB and the
+# partial sums' landing area 32 KB, which leaves 6 slots: 96 KB of weights in flight per SM,
+# against 160 KB at 16 rows.
+_CLUSTER_MAX_TOKENS = int(os.environ.get("BINFER_B200_CLUSTER_MAX_TOKENS", "32"))
 
 
 def cluster_token_limit() -> int:
