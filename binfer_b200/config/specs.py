@@ -33,6 +33,22 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class ScoreSpec:
+    """What is done to an attention score ``s = (q . k) * scale`` of query position p and key
+    position j before the softmax.  None of it is Qwen3's; a family whose attention has it
+    names it here, and the mixer takes the kernel that applies it.
+
+    ``softcap`` c > 0: ``s <- c * tanh(s / c)``.  ``slopes`` (one number per query head):
+    ``s <- s + slope_h * (j - p)``, a bias per distance.  ``sinks``: a learned logit per query
+    head (tensor ``sinks [heads]`` of the mixer) that joins the softmax's denominator and
+    takes no value: ``P_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j))``."""
+
+    softcap: float = 0.0
+    slopes: Optional[Tuple[float, ...]] = None
+    sinks: bool = False
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Grouped-query causal attention over a paged key/value cache."""
 
@@ -46,6 +62,7 @@ class AttentionSpec:
     window: Optional[int] = None  # keys j with p - window < j <= p; None = all keys
     scale: Optional[float] = None  # None = 1/sqrt(head_dim)
     position: Optional[object] = None   # RopeSpec, or any spec whose kind is registered
+    score: Optional[ScoreSpec] = None   # changes to the scores before the softmax; None: none
 
     @property
     def group_size(self) -> int:

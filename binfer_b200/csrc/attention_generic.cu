@@ -14,6 +14,11 @@
 // (cuda/kernels/bf16_kernels.cu:909-973; cuda/kernels/paged_attention.cu:408-487).
 // The reference reads prefill keys from the fresh projection, not the cache
 // (src/engine/batched_engine.ts:1082-1086); here every key comes from the pages.
+//
+// It is also where changes to the scores live, for attention that has them (the tuned
+// kernels take none): a soft cap s <- c tanh(s / c), a bias per distance s <- s +
+// slope_h (j - p), and a sink, a logit per head that joins the softmax's denominator and
+// carries no value.  All three are off with softcap 0 and null pointers.
 #include <float.h>
 
 #include "common.cuh"
@@ -25,7 +30,8 @@ __global__ void paged_attention_generic_kernel(
     const A* __restrict__ q, const A* __restrict__ k_cache, const A* __restrict__ v_cache,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ block_tables, int table_stride, A* __restrict__ out, int nh, int nkv,
-    int d, int page_size, int num_pages, int window, float scale, int* __restrict__ err) {
+    int d, int page_size, int num_pages, int window, float scale, float softcap,
+    const float* __restrict__ slopes, const float* __restrict__ sinks, int* __restrict__ err) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -67,6 +73,8 @@ __global__ void paged_attention_generic_kernel(
       float a = 0.f;
 #pragma unroll 8
       for (int i = 0; i < d; ++i) a += qs[i] * bf_ld(kr + i);
+      if (softcap > 0.f) a = softcap * tanhf(a / softcap);
+      if (slopes) a += slopes[h] * (float)(j - p);
       s = a;
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -89,6 +97,13 @@ __global__ void paged_attention_generic_kernel(
       }
     }
   }
+  if (sinks) {                                  // the sink: in the denominator only
+    const float m_new = fmaxf(m, sinks[h]);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sinks[h] - m_new);
+#pragma unroll
+    for (int c = 0; c < ATT_MAX_ACC; ++c) acc[c] *= corr;
+  }
   const float inv = 1.f / l;
   A* o = out + ((size_t)t * nh + h) * d;
 #pragma unroll
@@ -101,8 +116,8 @@ __global__ void paged_attention_generic_kernel(
 BF_EXPORT int bf_paged_attention_generic(
     const void* q, const void* k_cache, const void* v_cache, const int* seq_of_token,
     const int* positions, const int* block_tables, int table_stride, void* out, int T, int nh,
-    int nkv, int d, int page_size, int num_pages, int window, float scale, int act_dtype,
-    int* err, cudaStream_t stream) {
+    int nkv, int d, int page_size, int num_pages, int window, float scale, float softcap,
+    const float* slopes, const float* sinks, int act_dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (d > 32 * ATT_MAX_ACC || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
   const int warps = 4;
@@ -112,11 +127,11 @@ BF_EXPORT int bf_paged_attention_generic(
     paged_attention_generic_kernel<float><<<grid, warps * 32, smem, stream>>>(
         (const float*)q, (const float*)k_cache, (const float*)v_cache, seq_of_token, positions,
         block_tables, table_stride, (float*)out, nh, nkv, d, page_size, num_pages, window, scale,
-        err);
+        softcap, slopes, sinks, err);
   else
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         seq_of_token, positions, block_tables, table_stride, (__nv_bfloat16*)out, nh, nkv, d,
-        page_size, num_pages, window, scale, err);
+        page_size, num_pages, window, scale, softcap, slopes, sinks, err);
   return bf_launch_status();
 }

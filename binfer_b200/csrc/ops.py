@@ -219,15 +219,26 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             seq_of_token: torch.Tensor, positions: torch.Tensor,
                             block_tables: torch.Tensor, out: torch.Tensor, nh: int, nkv: int,
                             d: int, window: Optional[int], scale: float,
-                            err: torch.Tensor) -> None:
+                            err: torch.Tensor, softcap: float = 0.0,
+                            slopes: Optional[torch.Tensor] = None,
+                            sinks: Optional[torch.Tensor] = None) -> None:
+    """Attention of every token row over its request's pages, any sizes.  ``softcap``,
+    ``slopes`` (float32 ``[nh]``) and ``sinks`` (float32 ``[nh]``) change the scores as
+    ``config.specs.ScoreSpec`` says; by default nothing is changed."""
     T = q.shape[0]
     if d > 256:
         raise KernelError(f"attention: head_dim {d} is not supported (at most 256)")
+    for name, t in (("slopes", slopes), ("sinks", sinks)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.numel() != nh:
+                raise KernelError(f"attention: {name} must have one entry per query head")
     _run("paged_attention_generic", lib().bf_paged_attention_generic, 
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_of_token), _ptr(positions),
         _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(T), _c_int(nh),
         _c_int(nkv), _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
-        _c_int(window or 0), _c_float(scale), _c_int(_dtype_code(q)), _ptr(err), _stream())
+        _c_int(window or 0), _c_float(scale), _c_float(softcap), _ptr(slopes), _ptr(sinks),
+        _c_int(_dtype_code(q)), _ptr(err), _stream())
 
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128, 256)

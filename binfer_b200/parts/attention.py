@@ -11,7 +11,10 @@ product against the concatenated weight; norm, rotation and cache write are one
 kernel; and every key, also those of the step's own tokens, is read from the
 pages, so a prompt can be cut into portions anywhere and portions can share a
 step with decoded tokens (the reference's prefill ignores the cache, :1082-1086).
-An optional window restricts a query at p to keys in (p - window, p].
+An optional window restricts a query at p to keys in (p - window, p].  Changes to
+the scores before the softmax (``AttentionSpec.score``: a soft cap, a bias per
+distance, a sink logit per head) are not Qwen3's; a spec that names one gets the
+generic attention kernel, which applies them, in both precisions.
 """
 from __future__ import annotations
 
@@ -52,6 +55,11 @@ class GQAAttention(Mixer):
         self.position = (build_position(spec.position, spec.head_dim, env)
                          if spec.position is not None else None)
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.sinks = self.slopes = None
+        if spec.score is not None and spec.score.slopes is not None:
+            if len(spec.score.slopes) != spec.num_heads:
+                raise ValueError("score.slopes needs one slope per query head")
+            self.slopes = torch.tensor(spec.score.slopes, dtype=torch.float32, device=env.device)
         self._qkv_plans = {}
 
     # ----------------------------------------------------------------- weights
@@ -64,6 +72,8 @@ class GQAAttention(Mixer):
         if s.qk_norm:
             specs += [ParamSpec(p + "q_norm.weight", (s.head_dim,), init="norm", role="vector"),
                       ParamSpec(p + "k_norm.weight", (s.head_dim,), init="norm", role="vector")]
+        if s.score is not None and s.score.sinks:
+            specs.append(ParamSpec(p + "sinks", (s.num_heads,), init="norm", role="vector"))
         if self.position is not None:
             specs += self.position.param_specs(p)
         return specs
@@ -77,6 +87,8 @@ class GQAAttention(Mixer):
         if self.spec.qk_norm:
             self.q_norm = get(sp["q_norm.weight"])
             self.k_norm = get(sp["k_norm.weight"])
+        if self.spec.score is not None and self.spec.score.sinks:
+            self.sinks = get(sp["sinks"])
         if self.position is not None:
             self.position.load(get)
 
@@ -174,11 +186,14 @@ class GQAAttention(Mixer):
         """
         s = self.spec
         tables = ctx.block_tables[view.group]
-        fast = q.dtype == torch.bfloat16 and s.head_dim in ops.DECODE_HEAD_DIMS
+        fast = (q.dtype == torch.bfloat16 and s.head_dim in ops.DECODE_HEAD_DIMS
+                and s.score is None)
         if not fast:
             ops.paged_attention_generic(
                 q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, tables, out,
-                s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale, ctx.err)
+                s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale, ctx.err,
+                softcap=s.score.softcap if s.score is not None else 0.0,
+                slopes=self.slopes, sinks=self.sinks)
             return
         common = (s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.softmax_scale)
         if ctx.decode_only:

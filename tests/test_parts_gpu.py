@@ -432,3 +432,97 @@ def test_schedule_runs_a_layer_twice_and_shares_pages(cuda_device):
             rows.append(runner.step([StepItem("r", toks[a:a + n], list(range(n)))]).clone())
             a += n
         assert H.rel_err(torch.cat(rows).cpu(), want) < 2e-5, cuts
+
+
+def _plain_scored_attention(q, k, v, scale, softcap, slopes, sinks):
+    """softmax over keys j <= p of cap(q.k * scale) + slope_h (j - p), with a sink logit per
+    head in the denominator; plain and whole, for the test below."""
+    T, heads, d = q.shape
+    group = heads // k.shape[1]
+    pos = torch.arange(T)
+    out = torch.empty_like(q)
+    for h in range(heads):
+        s = (q[:, h] @ k[:, h // group].T) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if slopes is not None:
+            s = s + slopes[h] * (pos[None, :] - pos[:, None])
+        s = s.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+        if sinks is not None:
+            s = torch.cat([s, sinks[h].expand(T, 1)], dim=1)
+        p = torch.softmax(s, dim=-1)[:, :T]
+        out[:, h] = p @ v[:, h // group]
+    return out
+
+
+@pytest.mark.parametrize("dtype,tol,tol_rms", [(torch.float32, 2e-5, 5e-6),
+                                               (torch.bfloat16, 3e-2, 1e-2)])
+def test_attention_whose_scores_are_changed(cuda_device, dtype, tol, tol_rms):
+    """Attention that this architecture does not have, named by the spec alone: a soft cap on
+    the scores, a bias per distance, a sink logit per head (a tensor of the mixer).  One layer
+    with all three, one with the cap only, one plain; whole, in portions and token by token,
+    against a plain restatement.  The cap is low enough and the slopes steep enough that
+    leaving either out shows."""
+    from binfer_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, NormSpec, RopeSpec,
+                                    ScheduleEntry, ScoreSpec)
+    from binfer_b200.engine import make_runner
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.parts import build_model, param_specs_for
+    from binfer_b200.weights import TensorSource, random_tensors
+    norm, rope = NormSpec(eps=1e-6), RopeSpec(theta=1e4, rotary_dim=16)
+    slopes = (0.5, 0.25, 0.125, 0.0625)
+    scores = [ScoreSpec(softcap=0.6, slopes=slopes, sinks=True), ScoreSpec(softcap=0.3), None]
+    layers = [LayerSpec(mixer=AttentionSpec(num_heads=4, num_kv_heads=2, head_dim=16,
+                                            position=rope, score=sc),
+                        ffn=GatedMLPSpec(intermediate_size=24), norm=norm) for sc in scores]
+    spec = _toy_spec(layers, [ScheduleEntry(i) for i in range(3)], vocab=40, hidden=32)
+    names = [s.name for s in param_specs_for(spec)]
+    assert "model.layers.0.self_attn.sinks" in names and "model.layers.1.self_attn.sinks" not in names
+    env = _env(dtype)
+    # (weights small enough that the scores stay of order one: with a sharp softmax the
+    # bfloat16 rounding of this 32-wide model alone exceeds the bounds)
+    weights = random_tensors(param_specs_for(spec), seed=4, std=0.12, norm_std=0.1)
+    model = build_model(spec, env, TensorSource.from_dict(weights))
+    n = 41
+    toks = H.random_tokens(n, 40, 8)
+
+    w = {k: v.double() for k, v in weights.items()}
+    if dtype == torch.bfloat16:
+        w = {k: (v.to(torch.bfloat16).double() if v.dim() > 1 else v) for k, v in w.items()}
+    pos = torch.arange(n)
+    ang = P.rope_angles(pos, 16, 1e4)
+
+    def plain(with_scores=True):
+        x = P.embedding(torch.tensor(toks), w["model.embed_tokens.weight"])
+        for i, sc in enumerate(scores):
+            p = f"model.layers.{i}."
+            a = p + "self_attn."
+            h = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6)
+            q = P.apply_rope((h @ w[a + "q_proj.weight"].T).view(n, 4, 16), ang)
+            k = P.apply_rope((h @ w[a + "k_proj.weight"].T).view(n, 2, 16), ang)
+            v = (h @ w[a + "v_proj.weight"].T).view(n, 2, 16)
+            if sc is None or not with_scores:
+                att = P.causal_attention(q, k, v, 16 ** -0.5)
+            else:
+                att = _plain_scored_attention(
+                    q, k, v, 16 ** -0.5, sc.softcap,
+                    torch.tensor(sc.slopes, dtype=torch.float64) if sc.slopes else None,
+                    w[a + "sinks"] if sc.sinks else None)
+            x = x + att.reshape(n, -1) @ w[a + "o_proj.weight"].T
+            h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6)
+            x = x + P.swiglu_mlp(h, w, p + "mlp.")
+        return P.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+    want = plain()
+    assert H.rel_err(plain(with_scores=False), want) > 0.2, "the changes would not show"
+    for cuts in ([n], [6, 1, 2, 17, 15], [20] + [1] * 21):
+        runner = make_runner(model, env, page_size=4, num_pages=12, max_requests=2)
+        runner.add_request("r")
+        rows, at = [], 0
+        for c in cuts:
+            rows.append(runner.step([StepItem("r", toks[at:at + c], list(range(c)))]).clone())
+            at += c
+        runner.check_errors()
+        got = torch.cat(rows).float().cpu()
+        assert H.rel_err(got, want) < tol and H.rel_rms(got, want) < tol_rms, (
+            cuts, H.rel_err(got, want), H.rel_rms(got, want))
