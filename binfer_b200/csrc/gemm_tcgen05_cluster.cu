@@ -52,7 +52,8 @@ struct ClusterGemmParams {
   int stages;
   int issuers;                  // threads that issue tcgen05.mma, 1 or 2
   int mma_rows;                 // M of the tcgen05.mma: 128, or 64 (at most 32 token rows)
-  int tok_rows;                 // token rows fetched and reduced: 16, 32 or 64 (>= tokens)
+  int tok_rows;                 // token rows fetched and reduced: 8, 16, 32 or 64 (>= tokens)
+  int replicate;                // at most 8 tokens, shown in every lane quarter of tensor memory
   int tmem_cols;                // tensor memory columns the CTA allocates (a power of two)
   int acc_stride;               // columns between the two issuers' accumulators
   long long ldo;
@@ -281,7 +282,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         tc_fence_after();
         const uint32_t a_addr = smem_u32(tiles + (size_t)stage * stage_bytes);
-        const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+        // (replicate: every 8-row group of the product reads the tile's eight token rows)
+        const uint64_t a_desc = umma_desc_k_sw128_sbo(a_addr, p.replicate ? 0u : 1024u);
         const uint64_t b_desc = umma_desc_k_sw128(a_addr + a_bytes);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
@@ -300,18 +302,26 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // product; a 64-row product keeps rows 16 q .. 16 q + 15 in the first 16 lanes of quarter q
   // (so 64 token rows use all four quarters, 16 of them only warps 0 and 4).  Warps 1 to 3
   // come here when the last load or product is issued.
+  // With at most eight tokens every quarter holds them all (the product's 8-row groups read
+  // the same eight rows), and the eight warps take the 16-column chunks in turn: the sums
+  // leave tensor memory in a quarter of the time that two warps took (1.3 to 1.9 us of a
+  // product's 7 to 35).
   const int quarter = warp & 3;
   const int per = p.mma_rows == 64 ? 16 : 32;            // rows a lane quarter holds
-  if (quarter * per < p.tok_rows) {
-    const int row = lane < per ? quarter * per + lane : 1 << 20;
+  if (p.replicate || quarter * per < p.tok_rows) {
+    const int row = p.replicate ? (lane < 8 ? lane : 1 << 20)
+                                : (lane < per ? quarter * per + lane : 1 << 20);
     const uint32_t lanes = (uint32_t)(quarter * 32) << 16;
     const int width = kAct ? p.bn / 2 : p.bn;          // columns to walk: outputs or sums
     const int chunks = (width + 15) / 16, half = (chunks + 1) / 2;
-    const int c_begin = warp >= 4 ? half * 16 : 0, c_end = warp < 4 ? half * 16 : chunks * 16;
+    const int c_begin = p.replicate ? warp * 16 : warp >= 4 ? half * 16 : 0;
+    const int c_end = p.replicate || warp >= 4 ? chunks * 16 : half * 16;
+    const int c_step = p.replicate ? 8 * 16 : 16;
     // (SwiGLU form) the factor of this lane's row, worked out while the products run
     float factor = 1.f;
     if (kAct && p.rs.partials)
-      for (int t = quarter * per; t < p.tokens && t < (quarter + 1) * per; ++t) {
+      for (int t = p.replicate ? 0 : quarter * per;
+           t < p.tokens && t < (p.replicate ? 8 : (quarter + 1) * per); ++t) {
         const float ft = bf_row_factor(p.rs, t, lane);
         if (t == row) factor = ft;
       }
@@ -321,7 +331,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
     tc_fence_after();
     BF_TRACE_POINT(10 * BF_TR_GEMM + 5);
     const uint32_t my_recv = smem_u32(recv);
-    for (int c0 = c_begin; c0 < c_end && kAct; c0 += 16) {
+    for (int c0 = c_begin; c0 < c_end && kAct; c0 += c_step) {
       // gate columns c0.., up columns bn/2 + c0.. of both issuers' accumulators
       const int h = p.bn / 2;
       uint32_t g[16], u[16];
@@ -366,7 +376,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       }
     }
-    for (int c0 = c_begin; c0 < c_end && !kAct; c0 += 16) {
+    for (int c0 = c_begin; c0 < c_end && !kAct; c0 += c_step) {
       uint32_t r[16];
       if (have) {
         if (p.issuers == 2 && kc1 - kc0 >= 2) {          // with the second issuer's share
@@ -565,7 +575,12 @@ template <typename OutT, int FORM>
 int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p, long long ldx,
                    long long ldw, cudaStream_t stream) {
   CUtensorMap mx, mw;
-  p.tok_rows = p.tokens <= 16 ? 16 : p.tokens <= 32 ? 32 : 64;
+  static const int rows = getenv("BINFER_B200_GEMM_MMA_ROWS") ? atoi(getenv("BINFER_B200_GEMM_MMA_ROWS")) : 64;
+  static const int replicate = getenv("BINFER_B200_GEMM_REPLICATE") ? atoi(getenv("BINFER_B200_GEMM_REPLICATE")) : 1;
+  p.mma_rows = rows == 64 ? 64 : 128;
+  // (the q/k/v form shares its tile's rows out by token and is left as it was)
+  p.replicate = replicate && p.tokens <= 8 && p.q_out == nullptr ? 1 : 0;
+  p.tok_rows = p.replicate ? 8 : p.tokens <= 16 ? 16 : p.tokens <= 32 ? 32 : 64;
   int e = bf_make_tensor_map_bf16_2d(&mx, x, p.tokens, p.K, ldx, p.tok_rows, BK);
   if (e) return e;
   e = bf_make_tensor_map_bf16_2d(&mw, w, p.features, p.K, ldw, p.act_out ? p.bn / 2 : p.bn, BK);
@@ -595,8 +610,6 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   // the same, but a decode step is long enough to run into the board's power limit, and with
   // 128-row products for 8 tokens the SM clock settled near 1750 MHz instead of 1965 (36
   // layers, batch 8: 4.28 against 4.12 ms a step with every projection on this kernel).
-  static const int rows = getenv("BINFER_B200_GEMM_MMA_ROWS") ? atoi(getenv("BINFER_B200_GEMM_MMA_ROWS")) : 64;
-  p.mma_rows = rows == 64 ? 64 : 128;
   int need = p.issuers * p.bn, cols = 32;
   while (cols < need) cols *= 2;
   p.tmem_cols = cols;
