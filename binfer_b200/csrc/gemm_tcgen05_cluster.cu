@@ -54,6 +54,7 @@ struct ClusterGemmParams {
   int mma_rows;                 // M of the tcgen05.mma: 128, or 64 (at most 32 token rows)
   int tok_rows;                 // token rows fetched and reduced: 8, 16, 32 or 64 (>= tokens)
   int replicate;                // at most 8 tokens, shown in every lane quarter of tensor memory
+  int async_send;               // partial sums by st.async onto the owner's mbarrier (not q/k/v)
   int tmem_cols;                // tensor memory columns the CTA allocates (a power of two)
   int acc_stride;               // columns between the two issuers' accumulators
   long long ldo;
@@ -111,6 +112,23 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, f
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b),
                "f"(c), "f"(d)
                : "memory");
+}
+
+// The same store, asynchronous: it counts its 16 bytes on the mbarrier `bar` of the CTA that
+// holds `addr` (both addresses in the cluster's shared window), so the receiver knows when
+// everything sent to it has landed without the whole cluster meeting at a barrier.
+__device__ __forceinline__ void st_async_v4(uint32_t addr, uint32_t bar, float a, float b,
+                                            float c, float d) {
+  asm volatile(
+      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+      ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ---- the q/k/v form's epilogue: what a warp needs of a token, and the rotation
@@ -180,7 +198,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   uint64_t* full = reinterpret_cast<uint64_t*>(base);
   uint64_t* empty = full + CL_MAX_STAGES;
   uint64_t* acc_full = empty + CL_MAX_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* landed = acc_full + 1;                         // the partial sums sent to this CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(landed + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // recv[rank][token][slice column]: partial sums sent to this CTA, as the owner of a slice
   float* recv = reinterpret_cast<float*>(base + CL_BAR_BYTES);
@@ -208,9 +227,14 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
       mbar_init(empty + s, 1);
     }
     mbar_init(acc_full, min(p.issuers, max(kc1 - kc0, 1)));   // one arrival per issuing thread with work
+    mbar_init(landed, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // what this CTA, as the owner of a slice, will be sent: every rank's rows of it
+    if (p.async_send) mbar_expect_tx(landed, (uint32_t)(p.cluster * p.tokens * (p.bn / p.cluster) * 4));
   }
+  // (the peers learn that this barrier exists: waited for before the first send, long after)
+  if (p.async_send) cluster_arrive();
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
@@ -308,6 +332,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
   // product's 7 to 35).
   const int quarter = warp & 3;
   const int per = p.mma_rows == 64 ? 16 : 32;            // rows a lane quarter holds
+  if (p.async_send) cluster_wait();                      // every peer's landing barrier exists
+  const uint32_t landed_addr = smem_u32(landed);
   if (p.replicate || quarter * per < p.tok_rows) {
     const int row = p.replicate ? (lane < 8 ? lane : 1 << 20)
                                 : (lane < per ? quarter * per + lane : 1 << 20);
@@ -412,11 +438,20 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
         const int owner = c0 / slice, group = (c0 - owner * slice) / 4;
         const int at = ((rank * (slice / 4) + group) * p.tok_rows + row) * 4;
         const uint32_t dst = map_to_rank(my_recv + (uint32_t)(at * 4), (uint32_t)owner);
+        if (p.async_send) {
+          const uint32_t bar = map_to_rank(landed_addr, (uint32_t)owner);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          st_cluster_v4(dst + (uint32_t)(q * p.tok_rows * 16), __uint_as_float(r[4 * q]),
+          for (int q = 0; q < 4; ++q)
+            st_async_v4(dst + (uint32_t)(q * p.tok_rows * 16), bar, __uint_as_float(r[4 * q]),
                         __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
                         __uint_as_float(r[4 * q + 3]));
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            st_cluster_v4(dst + (uint32_t)(q * p.tok_rows * 16), __uint_as_float(r[4 * q]),
+                          __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                          __uint_as_float(r[4 * q + 3]));
+        }
       }
     }
     tc_fence_before();
@@ -453,7 +488,13 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
 
   // every thread of every CTA of the cluster: partials are in place after this
   BF_TRACE_POINT(10 * BF_TR_GEMM + 3);
-  cluster_sync_all();
+  if (p.async_send) {
+    // this CTA's slice has landed (a wait that gives up is flagged at the end; zeros or
+    // stale sums are then stored, as after any such wait)
+    mbar_wait(landed, 0, abort);
+  } else {
+    cluster_sync_all();
+  }
   BF_TRACE_POINT(10 * BF_TR_GEMM + 4);
 
   for (int it = turn * heads_per_tile; takes_turns && it < n_mine * heads_per_tile; ++it) {
@@ -567,8 +608,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_x,
                  "r"(TMEM_COLS)
                  : "memory");
   }
-  // no CTA may exit while a peer could still write into its shared memory: all writes
-  // happened before the cluster barrier above, so nothing more is needed here
+  // no CTA may exit while a peer could still write into its shared memory: every write to
+  // this CTA was counted on its landing barrier (or happened before the cluster barrier),
+  // which it has waited for above, so nothing more is needed here
 }
 
 template <typename OutT, int FORM>
@@ -580,6 +622,8 @@ int launch_cluster(const void* x, const void* w, OutT* out, ClusterGemmParams p,
   p.mma_rows = rows == 64 ? 64 : 128;
   // (the q/k/v form shares its tile's rows out by token and is left as it was)
   p.replicate = replicate && p.tokens <= 8 && p.q_out == nullptr ? 1 : 0;
+  static const int async_send = getenv("BINFER_B200_GEMM_ASYNC_SEND") ? atoi(getenv("BINFER_B200_GEMM_ASYNC_SEND")) : 1;
+  p.async_send = async_send && p.q_out == nullptr && p.act_out == nullptr ? 1 : 0;
   p.tok_rows = p.replicate ? 8 : p.tokens <= 16 ? 16 : p.tokens <= 32 ? 32 : 64;
   int e = bf_make_tensor_map_bf16_2d(&mx, x, p.tokens, p.K, ldx, p.tok_rows, BK);
   if (e) return e;
