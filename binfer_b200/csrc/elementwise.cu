@@ -294,20 +294,31 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
   const size_t n = (size_t)T * per_row;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t step = (size_t)gridDim.x * blockDim.x;
-  for (; i < n; i += step) {
+  // two chunks a trip, all four loads asked for before the first is used
+  for (; i < n; i += 2 * step) {
+    const size_t i2 = i + step;
+    const bool two = i2 < n;
     const size_t t = i / per_row, c = (i - t * per_row) * 8;
-    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c);
-    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
-    uint4 o4;
-    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+    const size_t t2 = two ? i2 / per_row : t, c2 = two ? (i2 - t2 * per_row) * 8 : c;
+    uint4 g4[2], u4[2];
+    g4[0] = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c);
+    u4[0] = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
+    g4[1] = *reinterpret_cast<const uint4*>(gu + t2 * 2 * I + c2);
+    u4[1] = *reinterpret_cast<const uint4*>(gu + t2 * 2 * I + I + c2);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-      o2[j] = __floats2bfloat162_rn(bf_silu_fast(g.x) * u.x, bf_silu_fast(g.y) * u.y);
+    for (int k = 0; k < 2; ++k) {
+      if (k == 1 && !two) break;
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4[k]);
+      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4[k]);
+      uint4 o4;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+        o2[j] = __floats2bfloat162_rn(bf_silu_fast(g.x) * u.x, bf_silu_fast(g.y) * u.y);
+      }
+      *reinterpret_cast<uint4*>(out + (k ? t2 * I + c2 : t * I + c)) = o4;
     }
-    *reinterpret_cast<uint4*>(out + t * I + c) = o4;
   }
 }
 

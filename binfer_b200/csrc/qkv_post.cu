@@ -119,13 +119,40 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
   const int fi = (lane & 15) * 4;
   const float4 wq = q_w ? *reinterpret_cast<const float4*>(q_w + lane * 4) : make_float4(1, 1, 1, 1);
   const float4 wk = k_w ? *reinterpret_cast<const float4*>(k_w + lane * 4) : make_float4(1, 1, 1, 1);
-  for (int hh = hh_first; hh < nh + 2 * nkv; hh += gridDim.y * warps) {
+  // what does not depend on the head stays in registers: the lane's sines and cosines, and
+  // where the token's keys and values go
+  float sn4[4], cs4[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    sn4[j] = sn_s[fi + j];
+    cs4[j] = cs_s[fi + j];
+  }
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+  const size_t kv_base = ((size_t)page * nkv * page_size + off) * D + lane * 4;
+  const size_t kv_head = (size_t)page_size * D;
+  // A warp's heads are asked for six at a time, before the first of them is used: with one
+  // load in flight per warp a block of 2048 tokens' worth moved 2 TB/s (25 us a layer).
+  constexpr int AHEAD = 6;
+  const int stride = gridDim.y * warps;
+  uint2 ahead[AHEAD];
+  for (int hh0 = hh_first; hh0 < nh + 2 * nkv; hh0 += AHEAD * stride) {
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      const int hh = hh0 + a * stride;
+      ahead[a] = make_uint2(0u, 0u);
+      if (hh == hh_first)
+        ahead[a] = raw_first;
+      else if (hh < nh + 2 * nkv && (hh < nh || slot >= 0))
+        ahead[a] = *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride +
+                                                   (size_t)hh * D + lane * 4);
+    }
+#pragma unroll
+    for (int n = 0; n < AHEAD; ++n) {
+    const int hh = hh0 + n * stride;
+    if (hh >= nh + 2 * nkv) break;
     const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
     if (!is_q && slot < 0) continue;
-    const uint2 raw = hh == hh_first
-                          ? raw_first
-                          : *reinterpret_cast<const uint2*>(qkv + (size_t)t * row_stride +
-                                                            (size_t)hh * D + lane * 4);
+    const uint2 raw = ahead[n];
     const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
     const float2 a = __bfloat1622float2(r2[0]), b = __bfloat1622float2(r2[1]);
     float x[4] = {a.x * row_factor, a.y * row_factor, b.x * row_factor, b.y * row_factor};
@@ -142,9 +169,8 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
-        const float sn = sn_s[fi + j], cs = cs_s[fi + j];
         // lower half: x[i] cos - x[i+64] sin;  upper half: x[i] sin + x[i+64] cos
-        x[j] = upper ? other * sn + x[j] * cs : x[j] * cs - other * sn;
+        x[j] = upper ? other * sn4[j] + x[j] * cs4[j] : x[j] * cs4[j] - other * sn4[j];
       }
     }
     uint2 o;
@@ -160,10 +186,8 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(
       continue;
     }
     const int h = is_k ? hh - nh : hh - nh - nkv;
-    const int page = slot / page_size, off = slot - page * page_size;
-    __nv_bfloat16* dst =
-        (is_k ? k_cache : v_cache) + (((size_t)page * nkv + h) * page_size + off) * D;
-    *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+    *reinterpret_cast<uint2*>((is_k ? k_cache : v_cache) + kv_base + (size_t)h * kv_head) = o;
+    }
   }
 }
 
@@ -187,7 +211,11 @@ BF_EXPORT int bf_qk_norm_rope_kv_write(
       ((uintptr_t)q_w & 15) == 0 && ((uintptr_t)k_w & 15) == 0) {
     const int block = total >= 16 ? 256 : 128;
     // few tokens: a warp per head; many: a block per token, which walks the heads (at 2048
-    // tokens a warp per head measured a third slower: the sines are then computed six times)
+    // tokens a warp per head measured a third slower: the sines are then computed six times).
+    // At 2048 tokens the kernel is bound by issue, not memory (ncu: 13.1 M warp instructions,
+    // issue slots 67 % busy, 18.5 us for 50 MB); most of them are a block's preamble, not the
+    // heads' arithmetic: a variant with eight elements a lane and two heads a warp executed
+    // 10.4 M and, with fewer warps resident, took 21.6 us.
     const int parts = T <= 64 ? (total * 32 + block - 1) / block : 1;
     return bf_launch_pdl(qk_norm_rope_kv_write_d128_kernel, dim3(T, parts), dim3(block), 0,
                          stream, (const __nv_bfloat16*)qkv,

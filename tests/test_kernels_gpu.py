@@ -135,6 +135,50 @@ def test_qk_norm_rope_kv_write(cuda_device, dtype, nh, nkv, d, rot, norm):
     assert float(kc.abs().sum(dim=(1, 3)).flatten().count_nonzero()) == T - 1
 
 
+@pytest.mark.parametrize("nh,nkv,norm", [(8, 2, True), (32, 8, True), (5, 1, True), (64, 8, True),
+                                         (3, 3, False)])
+def test_qk_norm_rope_kv_write_many_tokens(cuda_device, nh, nkv, norm):
+    """Heads of 128 and more than 64 tokens: a block per token whose warps walk the heads, six
+    of them asked for at a time.  Odd head counts, 80 heads; some tokens are not written;
+    positions are far apart."""
+    from binfer_b200.csrc import ops
+    T, d, ps, eps, theta = 203, 128, 16, 1e-6, 1e6
+    dev = cuda_device
+    g = torch.Generator().manual_seed(nh)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g).to(BF16).to(dev)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(dev) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(dev) if norm else None
+    pos = (torch.arange(T) * 37 % 5000).to(torch.int32).to(dev)
+    pages = T // ps + 3
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    slots[7] = slots[100] = -1
+    slots = slots.to(dev)
+    i = torch.arange(d // 2, dtype=torch.float64)
+    inv = (theta ** (-2.0 * i / d)).float().to(dev)
+    kc = torch.zeros(pages, nkv, ps, d, device=dev, dtype=BF16)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, nh * d, device=dev, dtype=BF16)
+    err = _err(dev)
+    ops.qk_norm_rope_kv_write(qkv, qw, kw, inv, pos, slots, q_out, kc, vc, nh, nkv, d, eps, err)
+    assert int(err.item()) == 0
+    x = qkv.double().cpu()
+    q = x[:, :nh * d].view(T, nh, d)
+    k = x[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+    v = x[:, (nh + nkv) * d:].view(T, nkv, d)
+    if norm:
+        q, k = P.rms_norm(q, qw.double().cpu(), eps), P.rms_norm(k, kw.double().cpu(), eps)
+    ang = P.rope_angles(pos.cpu(), d, theta)
+    q, k = P.apply_rope(q, ang), P.apply_rope(k, ang)
+    _close(q_out.view(T, nh, d), q, BF16)
+    sl = slots.cpu()
+    live = sl >= 0
+    got_k = kc.cpu()[sl[live] // ps, :, sl[live] % ps]
+    got_v = vc.cpu()[sl[live] // ps, :, sl[live] % ps]
+    _close(got_k, k[live], BF16)
+    _close(got_v, v[live], BF16)
+    assert int(kc.abs().sum(dim=(1, 3)).flatten().count_nonzero()) == int(live.sum())
+
+
 # ----------------------------------------------------------------------- attention
 def _paged(k, v, ps, dev, dtype, seed=0, neighbours=False):
     """Scatter dense k, v ``[n, nkv, d]`` of one request into shuffled pages (or, with
