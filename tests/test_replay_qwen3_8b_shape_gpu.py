@@ -71,10 +71,11 @@ class _Shape:
             self.models[dtype] = (model_from_dir(self.dir, env), env)
         return self.models[dtype]
 
-    def runner(self, dtype, page_size, num_pages, graphs=False):
+    def runner(self, dtype, page_size, num_pages, graphs=False, max_requests=8):
         from binfer_b200.engine import make_runner
         model, env = self.model(dtype)
-        r = make_runner(model, env, page_size=page_size, num_pages=num_pages, max_requests=8)
+        r = make_runner(model, env, page_size=page_size, num_pages=num_pages,
+                        max_requests=max_requests)
         if graphs:
             r.enable_decode_graphs(max_batch=8, max_seq_len=GRAPH_SEQ_LEN)
         return r
@@ -222,3 +223,49 @@ def test_six_requests_decode_together_from_the_bucket_of_eight(shape, dtype):
             num, den = num + float((lg - ex).pow(2).sum()), den + float(ex.pow(2).sum())
         bound = (num / den) ** 0.5
     _compare(got, ref, dtype, "8B sizes/six decoding together", bound)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_a_long_portion_beside_many_decoding_requests(shape, dtype):
+    """What a serving step looks like: twenty requests that decode one token each beside a
+    600-token portion of another request's prompt (which starts at position 100), in one
+    batch: the decode attention over a subset of rows, the prefill attention over the rest,
+    the products at 620 token rows.  Then four more such steps with shorter portions."""
+    lens = [33 + 3 * i for i in range(20)]
+    reqs = {f"s{i}": H.random_tokens(n + 5, VOCAB, 500 + i) for i, n in enumerate(lens)}
+    reqs["big"] = H.random_tokens(100 + 600 + 4 * 37, VOCAB, 999)
+    keep = lambda rid, p: (p >= len(reqs[rid]) - 6) if rid != "big" else p % 41 == 0   # noqa: E731
+    ref = {}
+    for rid, toks in reqs.items():
+        rows = [p for p in range(len(toks)) if keep(rid, p)]
+        lg = P.forward(shape.raw, shape.w64, toks, dtype=torch.float64, rows=rows)
+        ref[rid] = {p: lg[i] for i, p in enumerate(rows)}
+    steps = []
+    for rid, toks in reqs.items():              # the prompts first, each alone
+        n = 100 if rid == "big" else len(toks) - 5
+        steps.append({"step": len(steps), "entries": [
+            {"id": rid, "tokens": toks[:n], "want": list(range(n))}], "end": []})
+    at = 100
+    for k, portion in enumerate([600, 37, 37, 37, 37]):
+        entries = [{"id": "big", "tokens": reqs["big"][at:at + portion],
+                    "want": list(range(portion))}]
+        at += portion
+        for rid, toks in reqs.items():
+            if rid != "big":
+                entries.append({"id": rid, "tokens": [toks[len(toks) - 5 + k]], "want": [0]})
+        steps.append({"step": len(steps), "entries": entries,
+                      "end": list(reqs) if k == 4 else []})
+    steps = H.thin_wants(steps, keep)
+    runner = shape.runner(dtype, 16, H.peak_pages(steps, 16), max_requests=24)
+    got = H.run_trace(runner, steps)
+    bound = None
+    if dtype == torch.bfloat16:
+        num = den = 0.0
+        for rid, toks in reqs.items():
+            rows = sorted(ref[rid])
+            lg = P.forward(shape.raw, shape.w64, toks, dtype=torch.float64, rows=rows,
+                           round_to=torch.bfloat16)
+            ex = torch.stack([ref[rid][p] for p in rows])
+            num, den = num + float((lg - ex).pow(2).sum()), den + float(ex.pow(2).sum())
+        bound = (num / den) ** 0.5
+    _compare(got, ref, dtype, "8B sizes/a long portion beside twenty decoding requests", bound)
