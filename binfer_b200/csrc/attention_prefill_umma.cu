@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(AU_THREADS, 2)
 prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
                               const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v,
+                              const __grid_constant__ CUtensorMap map_k_run,
+                              const __grid_constant__ CUtensorMap map_v_run,
                               const int* __restrict__ items, const int* __restrict__ block_tables,
                               int table_stride, __nv_bfloat16* __restrict__ out, int nh, int nkv,
                               int page_size, int num_pages, int window, float scale_log2,
@@ -189,7 +191,21 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
       if (lane == 0)
         mbar_expect_tx(kv_full + buf, (uint32_t)__popc(live) * page_size * D * 4);
       __syncwarp();
-      if (wanted) {
+      // A tile whose pages lie one after the other in the pool (the pool hands them out
+      // so) comes as one box of all its pages per half, instead of one box per page.
+      const int page0 = __shfl_sync(0xffffffffu, page, 0);
+      const bool run = pages > 1 && __all_sync(0xffffffffu, lane >= pages ||
+                                                                (wanted && page == page0 + lane));
+      if (run) {
+        if (lane < 2 * HALVES) {
+          const int hh = lane >> 1;
+          if (lane & 1)
+            bf_tma_load_4d(vb + hh * KHALF_BYTES, &map_v_run, kv_full + buf, hh * 64, 0, g, page0);
+          else
+            bf_tma_load_4d(Ks + buf * KV_BYTES + hh * KHALF_BYTES, &map_k_run, kv_full + buf,
+                           hh * 64, 0, g, page0);
+        }
+      } else if (wanted) {
         const int y = (page * nkv + g) * page_size;
 #pragma unroll
         for (int hh = 0; hh < HALVES; ++hh) {
@@ -407,6 +423,13 @@ int launch_umma(const void* q, const void* k_cache, const void* v_cache, const i
   if (e) return e;
   e = bf_make_tensor_map_bf16_2d(&mv, v_cache, cache_rows, D, D, page_size, 64);
   if (e) return e;
+  CUtensorMap mkr, mvr;      // a whole tile of pages that follow one another
+  e = bf_make_tensor_map_pages_bf16(&mkr, k_cache, num_pages, nkv, page_size, D,
+                                    AU_BN / page_size);
+  if (e) return e;
+  e = bf_make_tensor_map_pages_bf16(&mvr, v_cache, num_pages, nkv, page_size, D,
+                                    AU_BN / page_size);
+  if (e) return e;
   constexpr int HALVES = D / 64;
   // Q, two stages of K and V, P apart only when it does not fit over a K tile, barriers
   const size_t smem = 1024 + (size_t)HALVES * 16384 + (size_t)4 * HALVES * 8192 +
@@ -421,7 +444,7 @@ int launch_umma(const void* q, const void* k_cache, const void* v_cache, const i
     configured = true;
   }
   dim3 grid((max_rows + AU_BM - 1) / AU_BM, nh, n_items);
-  kern<<<grid, AU_THREADS, smem, stream>>>(mq, mk, mv, items, block_tables, table_stride,
+  kern<<<grid, AU_THREADS, smem, stream>>>(mq, mk, mv, mkr, mvr, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
                                            window, scale * 1.4426950408889634f, err);
   return bf_launch_status();

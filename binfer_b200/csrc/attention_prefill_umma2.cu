@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(A2_THREADS, 1)
 prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                                const __grid_constant__ CUtensorMap map_k,
                                const __grid_constant__ CUtensorMap map_v,
+                               const __grid_constant__ CUtensorMap map_k_run,
+                               const __grid_constant__ CUtensorMap map_v_run,
                                const int* __restrict__ items,
                                const int* __restrict__ block_tables, int table_stride,
                                __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size,
@@ -205,7 +207,21 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
       if (lane == 0)
         mbar_expect_tx(kv_full + st, (uint32_t)__popc(live) * page_size * D * 4);
       __syncwarp();
-      if (wanted) {
+      // A tile whose pages lie one after the other in the pool (the pool hands them out
+      // so) comes as one box of all its pages per half, instead of one box per page.
+      const int page0 = __shfl_sync(0xffffffffu, page, 0);
+      const bool run = pages > 1 && __all_sync(0xffffffffu, lane >= pages ||
+                                                                (wanted && page == page0 + lane));
+      if (run) {
+        if (lane < 2 * HALVES) {
+          const int hh = lane >> 1;
+          if (lane & 1)
+            bf_tma_load_4d(vb + hh * KHALF_BYTES, &map_v_run, kv_full + st, hh * 64, 0, g, page0);
+          else
+            bf_tma_load_4d(Ks + st * KV_BYTES + hh * KHALF_BYTES, &map_k_run, kv_full + st,
+                           hh * 64, 0, g, page0);
+        }
+      } else if (wanted) {
         const int y = (page * nkv + g) * page_size;
 #pragma unroll
         for (int hh = 0; hh < HALVES; ++hh) {
@@ -472,6 +488,13 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
   if (e) return e;
   e = bf_make_tensor_map_bf16_2d(&mv, v_cache, cache_rows, A2_D, A2_D, page_size, 64);
   if (e) return e;
+  CUtensorMap mkr, mvr;      // a whole tile of pages that follow one another
+  e = bf_make_tensor_map_pages_bf16(&mkr, k_cache, num_pages, nkv, page_size, A2_D,
+                                    A2_BN / page_size);
+  if (e) return e;
+  e = bf_make_tensor_map_pages_bf16(&mvr, v_cache, num_pages, nkv, page_size, A2_D,
+                                    A2_BN / page_size);
+  if (e) return e;
   // two Q tiles, three stages of K and V, two P buffers, the exchange arrays, barriers
   const size_t smem = 1024 + (size_t)2 * 32768 + (size_t)2 * A2_STAGES * 16384 +
                       (size_t)2 * 16384 + 2 * 3 * 1024 + 256;
@@ -485,7 +508,7 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
     configured = true;
   }
   dim3 grid((max_rows + 2 * A2_BM - 1) / (2 * A2_BM), nh, n_items);
-  kern<<<grid, A2_THREADS, smem, stream>>>(mq, mk, mv, items, block_tables, table_stride,
+  kern<<<grid, A2_THREADS, smem, stream>>>(mq, mk, mv, mkr, mvr, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
                                            window, scale * 1.4426950408889634f,
                                            A2_STAGGER_CYCLES, err);

@@ -134,7 +134,7 @@ def prefill_attention(a):
     dev = torch.device("cuda:0")
     T, start, nh, nkv, d, ps = a.tokens, a.start, a.heads, a.kv_heads, a.head_dim, a.page_size
     ctx = start + T
-    (kc, vc, bt), = _paged_cache(dev, 1, ctx, nkv, d, ps, 1)
+    (kc, vc, bt), = _paged_cache(dev, 1, ctx, nkv, d, ps, 1, a.scattered)
     q = torch.randn(T, nh * d, device=dev, dtype=BF16)
     out = torch.empty_like(q)
     items = torch.tensor([[0, 0, T, start]], dtype=torch.int32, device=dev)

@@ -690,17 +690,21 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
     assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("ps,window", [(64, None), (16, 300), (8, None)])
+@pytest.mark.parametrize("ps,window,neighbours", [(64, None, False), (16, 300, False),
+                                                  (8, None, False), (16, None, True),
+                                                  (8, 300, True), (32, 100, True)])
 @pytest.mark.parametrize("variant", ["umma", "umma2"])
-def test_prefill_attention_long_portions(cuda_device, ps, window, variant):
+def test_prefill_attention_long_portions(cuda_device, ps, window, neighbours, variant):
     """Portions of many query tiles over many key tiles (the rings of stages wrap, the two
     query tiles of a block end on different key tiles), from the start of a prompt and from
-    its middle, with and without a window."""
+    its middle, with and without a window; over shuffled pages and over pages that lie side
+    by side in the pool, whose tiles come as one box (but for the tile a window cuts)."""
     from binfer_b200.csrc import ops
     nh, nkv, d = 4, 2, 128
     ctxs, qlens = [1500, 700, 1100], [900, 700, 257]
     q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
-                                                   qlens, window, True, seed=23)
+                                                   qlens, window, True, seed=23,
+                                                   neighbours=neighbours)
     items, row = [], 0
     for b, (n, ql) in enumerate(zip(ctxs, qlens)):
         items.append([b, row, ql, n - ql])
