@@ -42,6 +42,22 @@ static inline int bf_make_tensor_map_bf16_2d(CUtensorMap* map, const void* base,
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// The same for writing: boxes of box_rows x 64 bf16 leave shared memory (128-byte swizzle) for
+// a [rows, cols] matrix; what lies outside the matrix is not written.
+static inline int bf_make_tensor_map_bf16_2d_store(CUtensorMap* map, void* base, long long rows,
+                                                   long long cols, long long ld, int box_rows) {
+  BfEncodeTiledFn enc = bf_encode_tiled();
+  if (!enc) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 // The paged cache [pages, heads, page_size, d] (bf16) as a 4-d tensor, fetched in boxes of
 // `box_pages` whole pages of one head and 64 columns: {64, page_size, 1, box_pages}.  In
 // shared memory the box is box_pages * page_size rows of 128 bytes, page after page, in the
@@ -103,6 +119,23 @@ __device__ __forceinline__ void bf_tma_load_2d(void* smem_dst, const CUtensorMap
       "[%0], [%1, {%3, %4}], [%2];" ::"r"(bf_smem_u32(smem_dst)),
       "l"(map), "r"(bf_smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// A box from shared memory to the matrix, in this thread's current bulk group (x: column, a
+// multiple of 8 elements; no coordinate negative).
+__device__ __forceinline__ void bf_tma_store_2d(const CUtensorMap* map, const void* smem_src,
+                                                int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   map),
+               "r"(bf_smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bf_bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// until at most N of this thread's bulk groups have not yet read their shared memory
+template <int N>
+__device__ __forceinline__ void bf_bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 // (x: column, a multiple of 8 elements = 16 bytes; the other coordinates have no rule)
 __device__ __forceinline__ void bf_tma_load_4d(void* smem_dst, const CUtensorMap* map,

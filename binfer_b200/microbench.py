@@ -161,6 +161,9 @@ def gemm(a):
     if a.library:
         name = "gemm_library"
         fns = [lambda w=w: torch.mm(x, w.t(), out=out) for w in ws]
+    elif a.pair:
+        name = f"gemm_bf16_pair(bn={a.bn})"
+        fns = [lambda w=w: ops.gemm_bf16_pair(x, w, out, err, a.bn) for w in ws]
     elif a.cluster:
         name = f"gemm_bf16_cluster(bn={a.bn},cluster={a.cluster})"
         fns = [lambda w=w: ops.gemm_bf16_cluster(x, w, out, err, a.bn, a.cluster) for w in ws]
@@ -189,6 +192,9 @@ def swiglu(a):
             torch.mm(x, w.t(), out=gu)
             ops.silu_mul(gu, out)
         fns = [lambda w=w: two(w) for w in ws]
+    elif a.pair:
+        name = f"gemm_bf16_pair(gated,bn={a.bn})"
+        fns = [lambda w=w: ops.gemm_bf16_pair(x, w, out, err, a.bn, gated=True) for w in ws]
     else:
         bn = a.bn or ops.gemm_swiglu_plan(I, K, dev)[0]
         name = f"gemm_bf16_swiglu(bn={bn})"
@@ -301,6 +307,8 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0, help="feature rows per tile (0: chosen)")
     ap.add_argument("--library", action="store_true", help="time cuBLAS on the same product")
+    ap.add_argument("--pair", action="store_true",
+                    help="gemm, swiglu: the kernel on pairs of SMs (many token rows)")
     ap.add_argument("--cluster", type=int, default=0,
                     help="gemm: split K over clusters of this many CTAs (needs --bn)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host, no CUDA graph")

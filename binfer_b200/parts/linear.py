@@ -43,6 +43,30 @@ def _use_own(M: int, N: int, K: int) -> bool:
     return M <= 128 and N >= 65536
 
 
+# Fewest token rows from which the gated feed-forward product goes to the kernel on pairs of
+# SMs (``csrc/gemm_tcgen05_pair.cu``, the activation in its epilogue).  Measured against the
+# library's product followed by the activation kernel, 12288 outputs from 4096 inputs:
+# 54 against 41 us at 128 tokens, 56 / 53 at 256, 82 / 82 at 512, 152 / 156 at 1024,
+# 278 / 302 at 2048.  0: never.
+_PAIR_MIN_TOKENS = int(os.environ.get("BINFER_B200_PAIR_MIN_TOKENS", "1024"))
+# The plain products stay with the library under "auto": the pair kernel takes 74 / 50 / 148 us
+# where the library takes 71 / 46 / 136 (2048 tokens; q/k/v, output and down projection).
+_PAIR_PLAIN = os.environ.get("BINFER_B200_PAIR_PLAIN", "0") != "0"
+
+
+def pair_token_limit() -> int:
+    """Fewest token rows for which the gated product goes to the kernel on pairs of SMs
+    (0: never)."""
+    if _POLICY == "library":
+        return 0
+    return _PAIR_MIN_TOKENS if _POLICY == "auto" else 256
+
+
+def _use_pair(M: int, N: int, K: int) -> bool:
+    lim = pair_token_limit()
+    return (_PAIR_PLAIN or _POLICY == "own") and lim > 0 and M >= lim and 1024 <= N < 65536
+
+
 def _use_cluster(M: int, N: int, K: int) -> bool:
     # (at 24 tokens the library takes 6.14 against the kernel's 5.98 ms, at 32: 6.96 against 6.97)
     if _POLICY == "library" or M > cluster_token_limit():
@@ -100,6 +124,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                 out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
             if ops.gemm_bf16_cluster(x, w, out, ops.error_word(x.device), *plan):
                 return out
+    if _use_pair(M, N, K):
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+        if ops.gemm_bf16_pair(x, w, out, ops.error_word(x.device)):
+            return out
     if _use_own(M, N, K):
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)

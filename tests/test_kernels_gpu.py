@@ -622,6 +622,64 @@ def test_gemm_bf16_tcgen05(cuda_device, M, N, K, out_dtype):
         assert torch.equal(other, out), f"tile width {bn} changes the result"
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 300, 200), (130, 128, 64), (256, 6144, 4096),
+                                   (300, 1000, 520), (513, 2100, 2048), (700, 272, 72),
+                                   (2048, 4096, 1024), (1000, 40, 4104)])
+@pytest.mark.parametrize("out_dtype", [BF16, F32])
+def test_gemm_bf16_pair(cuda_device, M, N, K, out_dtype):
+    """The product on pairs of SMs: token counts on both sides of the 256-row tile and of a
+    CTA's 128 rows, widths and depths that are no multiple of the tile, more tiles than pairs
+    (the rings of stages and the two accumulators wrap), bfloat16 and float32 results."""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(BF16).to(cuda_device)
+    out = torch.full((M, N), 99.0, device=cuda_device, dtype=out_dtype)
+    err = ops.error_word(cuda_device)
+    assert ops.gemm_bf16_pair(x, w, out, err)
+    assert int(err.item()) == 0
+    ref = x.double().cpu() @ w.double().cpu().T
+    if out_dtype == BF16:
+        _close(out, ref, BF16)
+    else:
+        err_rel = float((out.double().cpu() - ref).abs().max() / ref.abs().max())
+        assert err_rel <= 4e-7 * math.sqrt(K), err_rel
+    # every tile width gives the same sums (one order of accumulation over K); the narrow
+    # ones leave by plain stores, multiples of 64 columns through shared memory and TMA stores
+    for bn in (32, 160, 192, 256):
+        other = torch.empty_like(out)
+        assert ops.gemm_bf16_pair(x, w, other, err, bn=bn)
+        assert torch.equal(other, out), f"tile width {bn} changes the result"
+    assert int(err.item()) == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(3, 96, 64), (256, 12288, 1024), (300, 1000, 520),
+                                   (1100, 3000, 2048), (129, 72, 4104), (2048, 1536, 4096)])
+def test_gemm_bf16_pair_gated(cuda_device, M, I, K):
+    """The stacked gate/up product with the activation in its epilogue: every output column
+    pairs its gate row with the up row of the same output, at widths that are no multiple of
+    the tile; the rows beyond a partial tile stay untouched."""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(2 * I, K, generator=g)).to(BF16).to(cuda_device)
+    w[I:] *= torch.linspace(0.5, 2.0, I, device=cuda_device).to(BF16).unsqueeze(1)   # up rows differ
+    buf = torch.full((M + 2, I), 99.0, device=cuda_device, dtype=BF16)
+    out = buf[:M]
+    err = ops.error_word(cuda_device)
+    assert ops.gemm_bf16_pair(x, w, out, err, gated=True)
+    assert int(err.item()) == 0
+    gu = x.double().cpu() @ w.double().cpu().T
+    ref = gu[:, :I] / (1 + torch.exp(-gu[:, :I])) * gu[:, I:]
+    _close(out, ref, BF16)
+    assert float(buf[M:].float().min()) == 99.0
+    for bn in (64, 192, 256):
+        other = torch.empty_like(out)
+        assert ops.gemm_bf16_pair(x, w, other, err, bn=bn, gated=True)
+        assert torch.equal(other, out), f"tile width {bn} changes the result"
+    assert int(err.item()) == 0
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take(cuda_device):
     from binfer_b200.csrc import ops
     x = torch.randn(4, 100, device=cuda_device).to(BF16)       # K not a multiple of 8
