@@ -43,7 +43,8 @@ struct PairParams {
   int bn;                      // accumulator columns per tile: a multiple of 16 (gated: 64)
   int stages;
   int gated;                   // 1: w is [2 features, K], gate rows first
-  int staged;                  // 1: results leave through shared memory and TMA stores (bf16)
+  int staged;                  // 1: results leave through shared memory and TMA stores
+  int accumulate;              // 1: out (float) += the product
   long long ldo;               // row stride of the output, in elements
   int* err;
 };
@@ -110,7 +111,15 @@ __device__ __forceinline__ float pair_silu(float g) { return __fdividef(g, 1.f +
 
 template <typename OutT>
 __device__ __forceinline__ void pair_store16(OutT* dst, const uint32_t (&r)[16], bool vec,
-                                             int valid) {
+                                             int valid, bool accumulate) {
+  if constexpr (sizeof(OutT) == 4) {
+    if (accumulate) {
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj)
+        if (jj < valid) dst[jj] += __uint_as_float(r[jj]);
+      return;
+    }
+  }
   if (vec && valid >= 16) {
     if constexpr (sizeof(OutT) == 2) {
       uint4 v0, v1;
@@ -289,21 +298,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       const int row0 = tt * PM + (int)rank * 128 + quarter * 32;
       const int t = row0 + lane;               // token of this thread
       if (p.staged) {
-        // 64 output columns at a time: into shared memory in the 128-byte swizzle, out by
-        // one TMA store per slab (whole lines; the matrix's edges are cut by the copy).
-        if constexpr (sizeof(OutT) == 2) {
-          const int row = quarter * 32 + lane;
-          const int slabs = p.gated ? 2 : p.bn >> 6;
-          for (int slab = 0; slab < slabs; ++slab) {
-            uint8_t* buf = out_stage + (n_stored & 1) * P_OUT_BYTES;
-            if (threadIdx.x == 64) bf_bulk_wait_read<1>();   // the store before last has read it
-            epilogue_sync();
+        // 128 bytes of every row at a time (64 bf16 or 32 floats): into shared memory in the
+        // 128-byte swizzle, out by one TMA store (or add) per slab: whole lines, the matrix's
+        // edges cut by the copy.
+        const int row = quarter * 32 + lane;
+        constexpr int SLAB = 128 / (int)sizeof(OutT);
+        const int slabs = p.gated ? 2 : p.bn / SLAB;
+        for (int slab = 0; slab < slabs; ++slab) {
+          uint8_t* buf = out_stage + (n_stored & 1) * P_OUT_BYTES;
+          if (threadIdx.x == 64) bf_bulk_wait_read<1>();   // the store before last has read it
+          epilogue_sync();
+          if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
             for (int hs = 0; hs < 2; ++hs) {
               uint32_t r[32];
               if (!p.gated) {
-                const int col = slab * 64 + hs * 32;
-                tmem_ld32(taddr + col, r);
+                tmem_ld32(taddr + slab * 64 + hs * 32, r);
               } else {
                 uint32_t up[32];
                 const int col = slab * 128 + hs * 32;
@@ -325,16 +335,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                 *reinterpret_cast<uint4*>(buf + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
               }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            epilogue_sync();
-            if (threadIdx.x == 64) {
-              const int x = p.gated ? tf * 128 + slab * 64 : tf * p.bn + slab * 64;
-              if (x < p.features && tt * PM + (int)rank * 128 < p.tokens)
-                bf_tma_store_2d(&map_out, buf, x, tt * PM + (int)rank * 128);
-              bf_bulk_commit();
-            }
-            ++n_stored;
+          } else {
+            uint32_t r[32];
+            tmem_ld32(taddr + slab * 32, r);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(buf + row * 128 + ((q ^ (row & 7)) << 4)) =
+                  make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          epilogue_sync();
+          if (threadIdx.x == 64) {
+            const int x = p.gated ? tf * 128 + slab * 64 : tf * p.bn + slab * SLAB;
+            const int y = tt * PM + (int)rank * 128;
+            if (x < p.features && y < p.tokens) {
+              if (p.accumulate)
+                bf_tma_reduce_add_2d(&map_out, buf, x, y);
+              else
+                bf_tma_store_2d(&map_out, buf, x, y);
+            }
+            bf_bulk_commit();
+          }
+          ++n_stored;
         }
       } else if (row0 < p.tokens) {          // uniform per warp: tcgen05.ld is warp-wide
         if (!p.gated) {
@@ -343,7 +365,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
             tmem_ld16(taddr + c0, r);
             const int f0 = tf * p.bn + c0;
             if (t < p.tokens && f0 < p.features)
-              pair_store16(out + (size_t)t * p.ldo + f0, r, vec_ok, p.features - f0);
+              pair_store16(out + (size_t)t * p.ldo + f0, r, vec_ok, p.features - f0, p.accumulate != 0);
           }
         } else {
           const int q = p.bn >> 2;
@@ -357,7 +379,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                 for (int j = 0; j < 16; ++j)
                   g[j] = __float_as_uint(pair_silu(__uint_as_float(g[j])) *
                                          __uint_as_float(up[j]));
-                pair_store16(out + (size_t)t * p.ldo + o0, g, vec_ok, p.features - o0);
+                pair_store16(out + (size_t)t * p.ldo + o0, g, vec_ok, p.features - o0, false);
               }
             }
         }
@@ -420,15 +442,15 @@ int launch(const void* x, const void* w, OutT* out, PairParams p, long long ldx,
   const int w_rows = p.gated ? 2 * p.features : p.features;
   e = bf_make_tensor_map_bf16_2d(&mw, w, w_rows, p.K, ldw, p.gated ? p.bn / 4 : p.bn / 2, BK);
   if (e) return e;
-  // Results leave through shared memory and TMA stores where the output is bf16 with rows that
-  // start on 16-byte boundaries and the tile is cut into slabs of 64 output columns.
+  // Results leave through shared memory and TMA stores where the output's rows start on
+  // 16-byte boundaries and the tile is cut into slabs of 128 bytes a row.
   CUtensorMap mo = mx;
   p.staged = 0;
   static const bool staged_ok =
       !getenv("BINFER_B200_PAIR_STAGED") || atoi(getenv("BINFER_B200_PAIR_STAGED")) != 0;
-  if (staged_ok && sizeof(OutT) == 2 && (p.ldo * 2) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
-      (p.gated ? p.bn == 256 : p.bn % 64 == 0)) {
-    e = bf_make_tensor_map_bf16_2d_store(&mo, out, p.tokens, p.features, p.ldo, 128);
+  if (staged_ok && (p.ldo * sizeof(OutT)) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
+      (p.gated ? p.bn == 256 : p.bn % (128 / (int)sizeof(OutT)) == 0)) {
+    e = bf_make_tensor_map_2d_store(&mo, out, p.tokens, p.features, p.ldo, 128, (int)sizeof(OutT));
     if (e) return e;
     p.staged = 1;
   }
@@ -496,15 +518,18 @@ BF_EXPORT int bf_gemm_pair_choose_bn(int tokens, int columns, int step, int num_
 // out[tokens, features] = x[tokens, K] * w[features, K]^T in bf16 with float accumulation, on
 // pairs of CTAs.  gated != 0: w is [2 features, K] (gate rows first) and out[t, o] =
 // silu(x . w[o]) * (x . w[features + o]), bf16 only.  out_dtype: BF_DTYPE_BF16 or
-// BF_DTYPE_F32.  bn: accumulator columns per tile (0: chosen here).  Returns
+// BF_DTYPE_F32.  accumulate != 0 (float out only): out += the product.  bn: accumulator
+// columns per tile (0: chosen here).  Returns
 // cudaErrorInvalidValue for shapes it does not take.
 BF_EXPORT int bf_gemm_bf16_pair(const void* x, const void* w, void* out, int tokens, int features,
                                 int K, long long ldx, long long ldw, long long ldo, int out_dtype,
-                                int gated, int bn, int num_sms, int* err, cudaStream_t stream) {
+                                int gated, int accumulate, int bn, int num_sms, int* err,
+                                cudaStream_t stream) {
   if (tokens <= 0 || features <= 0) return 0;
   if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || num_sms < 2)
     return (int)cudaErrorInvalidValue;
   if (gated && out_dtype != BF_DTYPE_BF16) return (int)cudaErrorInvalidValue;
+  if (accumulate && (gated || out_dtype != BF_DTYPE_F32)) return (int)cudaErrorInvalidValue;
   // (widths chosen here are multiples of 64: the slabs that leave through TMA stores)
   const int step = gated || bn <= 0 ? 64 : 16;
   const int columns = gated ? 2 * features : features;
@@ -517,6 +542,7 @@ BF_EXPORT int bf_gemm_bf16_pair(const void* x, const void* w, void* out, int tok
   p.ldo = ldo;
   p.bn = bn;
   p.gated = gated ? 1 : 0;
+  p.accumulate = accumulate ? 1 : 0;
   p.tiles_t = (tokens + PM - 1) / PM;
   p.tiles_f = (columns + bn - 1) / bn;
   p.stages = 0;

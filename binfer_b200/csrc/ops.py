@@ -403,14 +403,17 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: torch.Te
 
 
 def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
-                   bn: int = 0, gated: bool = False) -> bool:
+                   bn: int = 0, gated: bool = False, accumulate: bool = False) -> bool:
     """out[M, N] = x[M, K] @ w[N, K]^T on pairs of SMs (``tcgen05.mma.cta_group::2``, tiles of
     256 token rows): the product for many token rows.  ``gated``: ``w`` is the stacked
     ``[2 N, K]`` gate/up weight and ``out[M, N] = silu(x w_gate^T) * (x w_up^T)``, bfloat16
-    only.  ``bn``: accumulator columns per tile (0: chosen by the library).  Returns False,
-    having done nothing, for shapes the kernel does not take."""
+    only.  ``accumulate``: ``out`` (float32) ``+=`` the product.  ``bn``: accumulator columns
+    per tile (0: chosen by the library).  Returns False, having done nothing, for shapes the
+    kernel does not take."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_bf16_pair: operands must be bfloat16")
+    if accumulate and (gated or out.dtype != torch.float32):
+        raise KernelError("gemm_bf16_pair: accumulate needs a float32 output and no gate")
     M, K = x.shape
     N = out.shape[1]
     if (K % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8
@@ -421,8 +424,8 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: tor
         return False
     _run("gemm_bf16_pair", lib().bf_gemm_bf16_pair, _ptr(x), _ptr(w), _ptr(out), _c_int(M),
          _c_int(N), _c_int(K), _c_ll(x.stride(0)), _c_ll(w.stride(0)), _c_ll(out.stride(0)),
-         _c_int(_dtype_code(out)), _c_int(1 if gated else 0), _c_int(bn),
-         _c_int(num_sms(x.device)), _ptr(err), _stream())
+         _c_int(_dtype_code(out)), _c_int(1 if gated else 0), _c_int(1 if accumulate else 0),
+         _c_int(bn), _c_int(num_sms(x.device)), _ptr(err), _stream())
     return True
 
 

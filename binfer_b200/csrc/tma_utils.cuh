@@ -42,19 +42,24 @@ static inline int bf_make_tensor_map_bf16_2d(CUtensorMap* map, const void* base,
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-// The same for writing: boxes of box_rows x 64 bf16 leave shared memory (128-byte swizzle) for
-// a [rows, cols] matrix; what lies outside the matrix is not written.
-static inline int bf_make_tensor_map_bf16_2d_store(CUtensorMap* map, void* base, long long rows,
-                                                   long long cols, long long ld, int box_rows) {
+// The same for writing: boxes of box_rows x 128 bytes (64 bf16 or 32 floats: elem_bytes 2 or 4)
+// leave shared memory (128-byte swizzle) for a [rows, cols] matrix; what lies outside the
+// matrix is not written.
+static inline int bf_make_tensor_map_2d_store(CUtensorMap* map, void* base, long long rows,
+                                              long long cols, long long ld, int box_rows,
+                                              int elem_bytes) {
   BfEncodeTiledFn enc = bf_encode_tiled();
   if (!enc) return (int)cudaErrorNotSupported;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(map,
+                   elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
@@ -128,6 +133,15 @@ __device__ __forceinline__ void bf_tma_store_2d(const CUtensorMap* map, const vo
                    map),
                "r"(bf_smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
+}
+// The same, added to what the matrix holds (the element type is the map's).
+__device__ __forceinline__ void bf_tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src,
+                                                     int x, int y) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
+          "l"(map),
+      "r"(bf_smem_u32(smem_src)), "r"(x), "r"(y)
+      : "memory");
 }
 __device__ __forceinline__ void bf_bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -171,3 +171,4 @@ def linear_add_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
         return None
     return ops.gemm_bf16_cluster_add_norm(x, w, resid, norm_w, eps, ops.error_word(x.device),
                                           *plan)
+

@@ -653,6 +653,33 @@ def test_gemm_bf16_pair(cuda_device, M, N, K, out_dtype):
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(5, 96, 64), (300, 1000, 520), (1024, 4096, 2048),
+                                   (700, 2050, 72)])
+def test_gemm_bf16_pair_adds_into_a_float_matrix(cuda_device, M, N, K):
+    """``out += x w^T``: every element gets its sum once (through TMA reductions where the rows
+    start on 16-byte boundaries, by plain read-add-write otherwise), rows and columns beyond
+    the matrix are not touched, and a second call adds again."""
+    from binfer_b200.csrc import ops
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(BF16).to(cuda_device)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(BF16).to(cuda_device)
+    base = torch.randn(M + 3, N, generator=g).to(cuda_device)
+    buf = base.clone()
+    err = ops.error_word(cuda_device)
+    assert ops.gemm_bf16_pair(x, w, buf[:M], err, accumulate=True)
+    assert int(err.item()) == 0
+    prod = x.double().cpu() @ w.double().cpu().T
+    ref = base[:M].double().cpu() + prod
+    got = buf[:M].double().cpu()
+    assert float((got - ref).abs().max() / ref.abs().max()) <= 4e-7 * math.sqrt(K) + 1e-6
+    assert torch.equal(buf[M:], base[M:])
+    assert ops.gemm_bf16_pair(x, w, buf[:M], err, accumulate=True)
+    ref2 = ref + prod
+    assert float((buf[:M].double().cpu() - ref2).abs().max() / ref2.abs().max()) \
+        <= 8e-7 * math.sqrt(K) + 1e-6
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("M,I,K", [(3, 96, 64), (256, 12288, 1024), (300, 1000, 520),
                                    (1100, 3000, 2048), (129, 72, 4104), (2048, 1536, 4096)])
 def test_gemm_bf16_pair_gated(cuda_device, M, I, K):
