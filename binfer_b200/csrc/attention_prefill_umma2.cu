@@ -38,6 +38,7 @@
 #include <cuda.h>
 #include <float.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "tma_utils.cuh"
@@ -78,7 +79,7 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                                const int* __restrict__ block_tables, int table_stride,
                                __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size,
                                int num_pages, int window, float scale_log2, int stagger,
-                               int* __restrict__ err) {
+                               int p_tmem, int* __restrict__ err) {
   constexpr int D = A2_D;
   constexpr int HALVES = D / 64;
   constexpr int QHALF_BYTES = A2_BM * 128;               // 128 query rows of 128 bytes
@@ -259,7 +260,7 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                     idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(s_full + grp * 2 + (n & 1));
-        if (grp == 1) umma_commit(k_dead + n % A2_STAGES);   // tile A may then write P over K
+        if (grp == 1 && !p_tmem) umma_commit(k_dead + n % A2_STAGES);   // tile A may then write P over K
       };
       bool ok = mbar_wait(q_full, 0, abort) && mbar_wait(kv_full, 0, abort);
       // tile B starts about half a tile's softmax after tile A: the two groups then stay out
@@ -290,12 +291,22 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t p_addr = smem_u32(grp == 0 ? Ks + st * KV_BYTES : Pb + (n & 1) * P_BYTES);
         const uint32_t v_addr = smem_u32(Vs + st * KV_BYTES);
         const uint32_t d_addr = tmem_base + (uint32_t)(256 + grp * 128);
+        if (p_tmem) {
+          // P lies over the first 32 columns of the tile's S buffer, two keys a column
+          const uint32_t p_tm = tmem_base + (uint32_t)(grp * 128 + (n & 1) * A2_BN);
 #pragma unroll
-        for (int k = 0; k < A2_BN / 16; ++k) {
-          // 16 keys further: along K inside P's swizzled rows, two 8-row groups down in V
-          umma_bf16(d_addr, umma_desc_k_sw128(p_addr + (uint32_t)(k * 32)),
-                    umma_desc_mn_sw128(v_addr + (uint32_t)(k * 2048), KHALF_BYTES), idesc_o,
-                    (n > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < A2_BN / 16; ++k)
+            umma_bf16_a_tmem(d_addr, p_tm + (uint32_t)(k * 8),
+                             umma_desc_mn_sw128(v_addr + (uint32_t)(k * 2048), KHALF_BYTES),
+                             idesc_o, (n > 0 || k > 0) ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < A2_BN / 16; ++k) {
+            // 16 keys further: along K inside P's swizzled rows, two 8-row groups down in V
+            umma_bf16(d_addr, umma_desc_k_sw128(p_addr + (uint32_t)(k * 32)),
+                      umma_desc_mn_sw128(v_addr + (uint32_t)(k * 2048), KHALF_BYTES), idesc_o,
+                      (n > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(o_done + grp * 2 + (n & 1));
         umma_commit(kv_empty + st);          // this thread's share: K, V (and P_A) of the tile
@@ -382,8 +393,10 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
         lsum *= factor;
-        uint8_t* Ps;
-        if (grp == 0) {
+        uint8_t* Ps = nullptr;
+        if (p_tmem) {
+          // nothing to wait for: the S buffer is this tile's own
+        } else if (grp == 0) {
           Ps = Ks + ((n % A2_STAGES)) * KV_BYTES;          // over the K tile, dead once S_B is done too
           if (active_b)
             mbar_wait(k_dead + n % A2_STAGES, (uint32_t)(n / A2_STAGES) & 1u, abort);
@@ -407,17 +420,25 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
           __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
           packed[j >> 1] = *reinterpret_cast<uint32_t*>(&p2);
         }
-        // 32 keys = four 16-byte chunks of this row
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int c = half * 4 + q4;                     // chunk index along the 64 keys
-          uint8_t* dst = Ps + r * 128 + ((c ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1],
-                                                      packed[4 * q4 + 2], packed[4 * q4 + 3]);
-        }
         lsum += tsum;
-        // P is read by the tensor core through the async proxy
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (p_tmem) {
+          // P over the first 32 columns of S (every thread of the row has read its S: the
+          // barrier above lies between); 32 keys = 16 columns
+          tmem_st16(tmem_base + lane_addr + (uint32_t)(grp * 128 + (n & 1) * A2_BN + half * 16),
+                    packed);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        } else {
+          // 32 keys = four 16-byte chunks of this row
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int c = half * 4 + q4;                   // chunk index along the 64 keys
+            uint8_t* dst = Ps + r * 128 + ((c ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1],
+                                                        packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          }
+          // P is read by the tensor core through the async proxy
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
         tc_fence_before();
         mbar_arrive(p_full + grp * 2 + (n & 1));
       }
@@ -507,10 +528,12 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
+  static const int p_tmem =
+      getenv("BINFER_B200_ATTN_P_TMEM") ? atoi(getenv("BINFER_B200_ATTN_P_TMEM")) : 1;
   dim3 grid((max_rows + 2 * A2_BM - 1) / (2 * A2_BM), nh, n_items);
   kern<<<grid, A2_THREADS, smem, stream>>>(mq, mk, mv, mkr, mvr, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
                                            window, scale * 1.4426950408889634f,
-                                           A2_STAGGER_CYCLES, err);
+                                           A2_STAGGER_CYCLES, p_tmem, err);
   return bf_launch_status();
 }
