@@ -365,8 +365,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
           } else {
 #pragma unroll
             for (int c = 0; c < 8; ++c)
-#pragma unroll
-              for (int i = 0; i < 2; ++i) t2[i] = fmaxf(t2[i], __uint_as_float(v[4 * c + 2 * e + i]));
+              t2[c & 1] = max3f(t2[c & 1], __uint_as_float(v[4 * c + 2 * e]),
+                                __uint_as_float(v[4 * c + 2 * e + 1]));
           }
           float t = fmaxf(t2[0], t2[1]);
           t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 1));
@@ -411,20 +411,22 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int e = 0; e < 2; ++e) {
           lsum[e] *= factor[e];
           const float m_use = m_ref[e] == -INFINITY ? 0.f : m_ref[e];
-          float tsum = 0.f;
+          float ts0 = 0.f, ts1 = 0.f;
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            float e0 = ex2_approx(fmaf(__uint_as_float(v[4 * c + 2 * e]), scale_log2, -m_use));
-            float e1 = ex2_approx(fmaf(__uint_as_float(v[4 * c + 2 * e + 1]), scale_log2, -m_use));
+            float x0, x1;
+            fma2f(x0, x1, __uint_as_float(v[4 * c + 2 * e]), __uint_as_float(v[4 * c + 2 * e + 1]),
+                  scale_log2, -m_use);
+            float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
             if (need_mask[e]) {
               if (8 * c < lo[e] || 8 * c > hi[e]) e0 = 0.f;
               if (8 * c + 1 < lo[e] || 8 * c + 1 > hi[e]) e1 = 0.f;
             }
-            tsum += e0 + e1;
+            add2f(ts0, ts1, e0, e1);
             __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
             packed[2 * c + e] = *reinterpret_cast<uint32_t*>(&p2);
           }
-          lsum[e] += tsum;
+          lsum[e] += ts0 + ts1;
         }
         // P over the first 32 columns of S, in this warp's 16 lanes: scores it has read
         tmem_st_frag32(my_s + (uint32_t)((n & 1) * A2_BN), packed);

@@ -232,6 +232,35 @@ __device__ __forceinline__ void tmem_st_frag32(uint32_t taddr, const uint32_t (&
       : "memory");
 }
 
+// The maximum of three in one instruction, and two multiply-adds / two additions in one
+// (sm_100's three-input max and packed f32x2 arithmetic).
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (x0, x1) = (a0, a1) * s + m
+__device__ __forceinline__ void fma2f(float& x0, float& x1, float a0, float a1, float s, float m) {
+  asm("{\n\t.reg .b64 a, b, c, d;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "mov.b64 b, {%4, %4};\n\t"
+      "mov.b64 c, {%5, %5};\n\t"
+      "fma.rn.f32x2 d, a, b, c;\n\t"
+      "mov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(x0), "=f"(x1)
+      : "f"(a0), "f"(a1), "f"(s), "f"(m));
+}
+// (s0, s1) += (e0, e1)
+__device__ __forceinline__ void add2f(float& s0, float& s1, float e0, float e1) {
+  asm("{\n\t.reg .b64 a, b;\n\t"
+      "mov.b64 a, {%0, %1};\n\t"
+      "mov.b64 b, {%2, %3};\n\t"
+      "add.rn.f32x2 a, a, b;\n\t"
+      "mov.b64 {%0, %1}, a;\n\t}"
+      : "+f"(s0), "+f"(s1)
+      : "f"(e0), "f"(e1));
+}
+
 // 2^x by the special-function unit (x <= 0 here; -inf gives 0)
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
