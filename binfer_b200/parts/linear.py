@@ -91,6 +91,22 @@ _CLUSTER_MAX_FEATURES = int(os.environ.get("BINFER_B200_CLUSTER_MAX_FEATURES", "
 _CLUSTER_MAX_TOKENS = int(os.environ.get("BINFER_B200_CLUSTER_MAX_TOKENS", "32"))
 
 
+# ... and for the gate/up projection with the activation in its epilogue (the same kernel, on
+# "clusters" of one CTA).  Inside a step against the library's product followed by the
+# activation kernel: a tie from 33 to 56 rows (7.06 / 7.07 ms at 33, 8.72 / 8.69 at 48,
+# 9.62 / 9.62 at 56), 10.45 against 10.56 ms at 64.  The other three products at 64 rows each
+# cost 0.2 ms a step against the library (10.75 to 10.80 ms).
+_SWIGLU_MAX_TOKENS = int(os.environ.get("BINFER_B200_SWIGLU_MAX_TOKENS", "64"))
+
+
+def swiglu_token_limit() -> int:
+    """Most token rows for which the gate/up projection runs on the cluster kernel's gated form."""
+    if _POLICY == "library":
+        return 0
+    return min(_SWIGLU_MAX_TOKENS, ops.CLUSTER_MAX_TOKENS) if _POLICY == "auto" \
+        else ops.CLUSTER_MAX_TOKENS
+
+
 def cluster_token_limit() -> int:
     """Most token rows for which the policy sends products to the split-K cluster kernel."""
     if _POLICY == "library":

@@ -17,7 +17,7 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import (BuildEnv, DeferredLinear, FeedForward, ScaledRows, StepContext, register_ffn,
                    split_scaled)
-from .linear import cluster_token_limit, linear, pair_token_limit
+from .linear import linear, pair_token_limit, swiglu_token_limit
 
 # BINFER_B200_FUSE_SWIGLU=0: the stacked gate/up projection and the activation as two kernels
 FUSE_SWIGLU = os.environ.get("BINFER_B200_FUSE_SWIGLU", "1") != "0"
@@ -73,7 +73,7 @@ class GatedMLP(FeedForward):
         if pair_from and x.shape[0] >= pair_from and row_scale is None:
             # many token rows: the product on pairs of SMs, the activation in its epilogue
             return ops.gemm_bf16_pair(x, self.w_gate_up, h, ops.error_word(x.device), gated=True)
-        if x.shape[0] > cluster_token_limit():
+        if x.shape[0] > swiglu_token_limit():
             return False
         if self._swiglu_plan is None:
             self._swiglu_plan = ops.gemm_swiglu_plan(self.inter, x.shape[1], x.device) or False
