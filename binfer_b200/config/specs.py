@@ -142,6 +142,19 @@ class NameLayout:
     ffn: str = "mlp"
     final_norm: str = "model.norm.weight"
     lm_head: str = "lm_head.weight"
+    # further norms of a layer, for arrangements that have more than the two above:
+    # (role, name inside the layer) pairs
+    more_norms: Tuple[Tuple[str, str], ...] = ()
+
+    def norm(self, role: str) -> str:
+        """The name, inside a layer, of the norm that plays ``role``: ``input``,
+        ``post_mixer`` or one of ``more_norms``."""
+        table = {"input": self.input_norm, "post_mixer": self.post_mixer_norm,
+                 **dict(self.more_norms)}
+        if role not in table:
+            raise KeyError(f"no norm with the role {role!r} in this family's names "
+                           f"(known: {sorted(table)})")
+        return table[role]
 
 
 class ConfigError(ValueError):

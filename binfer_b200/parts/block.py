@@ -20,10 +20,10 @@ class PreNormBlock(Part):
                  env: BuildEnv):
         p = names.layer_prefix.format(i=index)
         self.index = index
-        self.input_norm = build_norm(spec.norm, hidden_size, f"{p}{names.input_norm}.weight", env)
+        self.input_norm = build_norm(spec.norm, hidden_size, f"{p}{names.norm('input')}.weight", env)
         self.mixer = build_mixer(spec.mixer, hidden_size, f"{p}{names.mixer}.", env)
         self.post_norm = build_norm(spec.norm, hidden_size,
-                                    f"{p}{names.post_mixer_norm}.weight", env)
+                                    f"{p}{names.norm('post_mixer')}.weight", env)
         self.ffn = build_ffn(spec.ffn, hidden_size, f"{p}{names.ffn}.", env)
 
     def parts(self) -> List[Part]:

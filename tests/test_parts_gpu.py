@@ -378,6 +378,114 @@ def test_toy_position_encodings(cuda_device, dtype, tol, tol_rms):
         assert H.rel_err(got, want) < tol and H.rel_rms(got, want) < tol_rms, cuts
 
 
+def _register_sandwich_block():
+    """An arrangement of a layer's parts that the framework does not ship: every sublayer has a
+    norm before it and one after it (``x += norm_b(mixer(norm_a(x)))``), four norms a layer,
+    whose names come from the family's :class:`NameLayout`."""
+    from binfer_b200.parts import build_ffn, build_mixer, build_norm, register_block
+    from binfer_b200.parts.base import ResidualStream
+
+    class SandwichBlock:
+        def __init__(self, spec, hidden, names, index, env):
+            p = names.layer_prefix.format(i=index)
+            self.norms = {role: build_norm(spec.norm, hidden, f"{p}{names.norm(role)}.weight", env)
+                          for role in ("input", "post_mixer", "pre_ffn", "post_ffn")}
+            self.mixer = build_mixer(spec.mixer, hidden, f"{p}{names.mixer}.", env)
+            self.ffn = build_ffn(spec.ffn, hidden, f"{p}{names.ffn}.", env)
+
+        def parts(self):
+            return [*self.norms.values(), self.mixer, self.ffn]
+
+        def param_specs(self):
+            return [s for part in self.parts() for s in part.param_specs()]
+
+        def load(self, get):
+            for part in self.parts():
+                part.load(get)
+
+        def _normed(self, role, h):
+            """The norm ``role`` of a sublayer's output (a tensor, not the stream)."""
+            return self.norms[role].forward(ResidualStream(h.float().contiguous()))
+
+        def forward(self, stream, ctx, view):
+            h = self.mixer.forward(self.norms["input"].forward(stream), ctx, view)
+            stream.add(self._normed("post_mixer", h))
+            h = self.ffn.forward(self.norms["pre_ffn"].forward(stream), ctx)
+            stream.add(self._normed("post_ffn", h))
+
+    register_block("test_sandwich", SandwichBlock)
+
+
+@pytest.mark.parametrize("dtype,tol,tol_rms", [(torch.float32, 2e-5, 5e-6),
+                                               (torch.bfloat16, 3e-2, 1e-2)])
+def test_toy_block_arrangement(cuda_device, dtype, tol, tol_rms):
+    """Another arrangement of a layer's parts, registered here, beside the shipped one in one
+    model: its four norms get their names from the family's layout, the weights load by those
+    names, and whole and cut prompts agree with a plain restatement."""
+    from binfer_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NameLayout,
+                                    NormSpec, RopeSpec, ScheduleEntry)
+    from binfer_b200.engine import make_runner
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.parts import build_model, param_specs_for
+    from binfer_b200.weights import TensorSource, random_tensors
+    _register_sandwich_block()
+    norm = NormSpec(eps=1e-6)
+    rope = RopeSpec(theta=50.0)
+    attn = AttentionSpec(num_heads=4, num_kv_heads=2, head_dim=16, position=rope)
+    layers = [LayerSpec(mixer=attn, ffn=GatedMLPSpec(intermediate_size=24), norm=norm,
+                        block="test_sandwich"),
+              LayerSpec(mixer=attn, ffn=GatedMLPSpec(intermediate_size=40), norm=norm)]
+    names = NameLayout(more_norms=(("pre_ffn", "pre_feedforward_layernorm"),
+                                   ("post_ffn", "post_feedforward_layernorm")))
+    spec = ModelSpec(architecture="ToySandwichForCausalLM", hidden_size=32, vocab_size=40,
+                     layers=tuple(layers), schedule=(ScheduleEntry(0), ScheduleEntry(1)),
+                     final_norm=NormSpec(eps=1e-5), tie_word_embeddings=True, names=names)
+    wanted = [s.name for s in param_specs_for(spec)]
+    assert "model.layers.0.pre_feedforward_layernorm.weight" in wanted
+    assert "model.layers.0.post_feedforward_layernorm.weight" in wanted
+    assert "model.layers.1.pre_feedforward_layernorm.weight" not in wanted
+    with pytest.raises(KeyError, match="known"):
+        NameLayout().norm("pre_ffn")
+    env = _env(dtype)
+    weights = random_tensors(param_specs_for(spec), seed=4, std=0.1, norm_std=0.05)
+    model = build_model(spec, env, TensorSource.from_dict(weights))
+    n = 17
+    toks = H.random_tokens(n, 40, 8)
+
+    w = {k: v.double() for k, v in weights.items()}
+    if dtype == torch.bfloat16:
+        w = {k: v.to(torch.bfloat16).double() for k, v in w.items()}
+    pos = torch.arange(n)
+    ang = P.rope_angles(pos, 16, 50.0)
+    x = P.embedding(torch.tensor(toks), w["model.embed_tokens.weight"])
+
+    def attention(h, a):
+        q = (h @ w[a + "q_proj.weight"].T).view(n, 4, 16)
+        k = (h @ w[a + "k_proj.weight"].T).view(n, 2, 16)
+        v = (h @ w[a + "v_proj.weight"].T).view(n, 2, 16)
+        q, k = P.apply_rope(q, ang), P.apply_rope(k, ang)
+        return P.causal_attention(q, k, v, 16 ** -0.5).reshape(n, -1) @ w[a + "o_proj.weight"].T
+
+    p0, p1 = "model.layers.0.", "model.layers.1."
+    h = attention(P.rms_norm(x, w[p0 + "input_layernorm.weight"], 1e-6), p0 + "self_attn.")
+    x = x + P.rms_norm(h, w[p0 + "post_attention_layernorm.weight"], 1e-6)
+    h = P.swiglu_mlp(P.rms_norm(x, w[p0 + "pre_feedforward_layernorm.weight"], 1e-6), w, p0 + "mlp.")
+    x = x + P.rms_norm(h, w[p0 + "post_feedforward_layernorm.weight"], 1e-6)
+    x = x + attention(P.rms_norm(x, w[p1 + "input_layernorm.weight"], 1e-6), p1 + "self_attn.")
+    x = x + P.swiglu_mlp(P.rms_norm(x, w[p1 + "post_attention_layernorm.weight"], 1e-6), w, p1 + "mlp.")
+    want = P.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+    for cuts in ([n], [5, 2, 1, 9]):
+        runner = make_runner(model, env, page_size=4, num_pages=10, max_requests=1)
+        runner.add_request("r")
+        rows, at = [], 0
+        for c in cuts:
+            rows.append(runner.step([StepItem("r", toks[at:at + c], list(range(c)))]).clone())
+            at += c
+        got = torch.cat(rows).float().cpu()
+        assert H.rel_err(got, want) < tol and H.rel_rms(got, want) < tol_rms, cuts
+
+
 def test_schedule_runs_a_layer_twice_and_shares_pages(cuda_device):
     """The order of execution is data: layer 0 runs twice (two caches of its own), and the
     last entry reads the pages that the first one wrote."""
