@@ -80,7 +80,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                                const int* __restrict__ items,
                                const int* __restrict__ block_tables, int table_stride,
                                __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size,
-                               int num_pages, int window, float scale_log2,
+                               int num_pages, int window, float scale_log2, int splits,
+                               float* __restrict__ part_o, float* __restrict__ part_ml,
                                int* __restrict__ err) {
   constexpr int D = A2_D;
   constexpr int HALVES = D / 64;
@@ -94,8 +95,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
   uint8_t* Qs = base;                                    // [2][Q_BYTES]
   uint8_t* Ks = Qs + 2 * Q_BYTES;                        // [STAGES][KV_BYTES]
   uint8_t* Vs = Ks + A2_STAGES * KV_BYTES;               // [STAGES][KV_BYTES]
-  float* xm = reinterpret_cast<float*>(Vs + A2_STAGES * KV_BYTES);   // [2 groups][128] row sums
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xm + 2 * 128);
+  float* xm = reinterpret_cast<float*>(Vs + A2_STAGES * KV_BYTES);   // [sums, references][2 groups][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xm + 4 * 128);
   uint64_t* q_full = bars;                     // [1]
   uint64_t* kv_full = bars + 1;                // [STAGES]
   uint64_t* kv_empty = kv_full + A2_STAGES;    // [STAGES]
@@ -105,7 +106,10 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 4);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int* it = items + 4 * blockIdx.z;
+  // with splits > 1 the keys of a block are shared out over `splits` CTAs, each of which leaves
+  // an unnormalised O with its exponent reference and sum for the merge kernel below
+  const int split = splits > 1 ? (int)blockIdx.z % splits : 0;
+  const int* it = items + 4 * (splits > 1 ? (int)blockIdx.z / splits : (int)blockIdx.z);
   const int seq = it[0], row0 = it[1], qlen = it[2], pos0 = it[3];
   // the last query blocks see the most keys: they are launched first
   const int qb = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
@@ -120,9 +124,15 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
   const int p_last_a = min(pos0 + qlen - 1, p_first + A2_BM - 1);
   const int p_last = active_b ? min(pos0 + qlen - 1, p_first + 2 * A2_BM - 1) : p_last_a;
   const int j_lo = window > 0 ? max(0, p_first - window + 1) : 0;
-  const int kt_first = j_lo / A2_BN;
-  const int tiles_a = p_last_a / A2_BN - kt_first + 1;
-  const int tiles = p_last / A2_BN - kt_first + 1;
+  int kt_first = j_lo / A2_BN;
+  int tiles_a = p_last_a / A2_BN - kt_first + 1;
+  int tiles = p_last / A2_BN - kt_first + 1;
+  if (splits > 1) {                                       // this CTA's share of the key tiles
+    const int b = tiles * split / splits, e = tiles * (split + 1) / splits;
+    kt_first += b;
+    tiles_a = max(0, min(tiles_a, e) - b);
+    tiles = e - b;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -154,7 +164,7 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
 
   if (warp == A2_TMA_WARP) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (lane == 0 && tiles > 0) {                        // (a share of the keys may be empty)
       mbar_expect_tx(q_full, 2 * Q_BYTES);
 #pragma unroll
       for (int t = 0; t < 2; ++t)
@@ -248,7 +258,7 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
     // tensor memory; they share the K and V tiles, which are released when both have arrived.
     const int grp = warp - A2_MMA_WARP;
     const int my_tiles = grp == 0 ? tiles_a : (active_b ? tiles : 0);
-    if (lane == 0 && my_tiles > 0) {
+    if (lane == 0) {
       // S: a = Q (K-major), b = K tile (K-major), N = 64 keys
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) |
                                ((uint32_t)(A2_BN >> 3) << 17) | ((uint32_t)(A2_BM >> 4) << 24);
@@ -268,8 +278,8 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         umma_commit(s_full + grp * 2 + (n & 1));
       };
-      bool ok = mbar_wait(q_full, 0, abort) && mbar_wait(kv_full, 0, abort);
-      if (ok) {
+      bool ok = my_tiles == 0 || (mbar_wait(q_full, 0, abort) && mbar_wait(kv_full, 0, abort));
+      if (ok && my_tiles > 0) {
         tc_fence_after();
         issue_s(0);
       }
@@ -442,9 +452,12 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         lsum[e] += __shfl_xor_sync(0xffffffffu, lsum[e], 2);
       }
       float* xl = xm + grp * 128;
+      float* xr = xm + 256 + grp * 128;                    // the rows' exponent references
       if (q4 == 0) {
         xl[wq * 32 + hb * 16 + (lane >> 2)] = lsum[0];
         xl[wq * 32 + hb * 16 + (lane >> 2) + 8] = lsum[1];
+        xr[wq * 32 + hb * 16 + (lane >> 2)] = m_ref[0];
+        xr[wq * 32 + hb * 16 + (lane >> 2) + 8] = m_ref[1];
       }
       // O leaves row by row: thread r of a quarter takes row r, each of the two warps of a
       // quarter one half of its columns
@@ -459,7 +472,26 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
                 mbar_wait(my_o_done + ((my_tiles - 1) & 1), (uint32_t)((my_tiles - 1) >> 1) & 1u,
                           abort);
       ok = group_all(bar_id, ok);
-      if (ok) {
+      if (ok && splits > 1) {
+        // unnormalised, for the merge: O in float, the reference and the sum beside it
+        tc_fence_after();
+        const size_t slot = ((size_t)(row0 + l) * nh + h) * splits + split;
+        float* dst = part_o + slot * D + half * OH;
+#pragma unroll 1
+        for (int c0 = 0; c0 < OH; c0 += 32) {
+          uint32_t w[32];
+          tmem_ld32(my_o + c0, w);
+          if (valid) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4)
+              *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(w[c], w[c + 1], w[c + 2], w[c + 3]);
+          }
+        }
+        if (valid && half == 0) {
+          part_ml[slot * 2] = xr[r];
+          part_ml[slot * 2 + 1] = xl[r];
+        }
+      } else if (ok) {
         tc_fence_after();
         const float inv = 1.f / xl[r];
         __nv_bfloat16* dst = out + ((size_t)(row0 + l) * nh + h) * D + half * OH;
@@ -482,6 +514,14 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       tc_fence_before();
+    } else if (splits > 1 && (grp == 0 || active_b) && ((warp >> 2) & 1) == 0) {
+      // no key tile of this share for the group's rows: a partial that the merge passes over
+      const int l = qb * 2 * A2_BM + grp * A2_BM + (warp & 3) * 32 + lane;
+      if (l < qlen) {
+        const size_t slot = ((size_t)(row0 + l) * nh + h) * splits + split;
+        part_ml[slot * 2] = -INFINITY;
+        part_ml[slot * 2 + 1] = 0.f;
+      }
     }
   }
 
@@ -495,17 +535,57 @@ prefill_attention_umma2_kernel(const __grid_constant__ CUtensorMap map_q,
   }
 }
 
+// The splits of a (query row, head) made one: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),
+// M the largest reference.  A warp per (row, head), a lane four of the 128 columns, the splits
+// in ascending order.
+__global__ void prefill_attention_merge_kernel(const float* __restrict__ part_o,
+                                               const float* __restrict__ part_ml,
+                                               const int* __restrict__ items,
+                                               __nv_bfloat16* __restrict__ out, int nh, int splits) {
+  const int* it = items + 4 * blockIdx.z;
+  const int row0 = it[1], qlen = it[2];
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), h = blockIdx.y, lane = threadIdx.x & 31;
+  if (r >= qlen) return;
+  const size_t base = ((size_t)(row0 + r) * nh + h) * splits;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float L = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < splits; ++s) {
+    const float m = part_ml[(base + s) * 2];
+    if (m == -INFINITY) continue;                          // a share without keys for this row
+    const float w = exp2f(m - M);
+    L += part_ml[(base + s) * 2 + 1] * w;
+    const float4 o = *reinterpret_cast<const float4*>(part_o + (base + s) * A2_D + lane * 4);
+    acc.x += o.x * w;
+    acc.y += o.y * w;
+    acc.z += o.z * w;
+    acc.w += o.w * w;
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  uint2 packed;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+  o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+  o2[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out + ((size_t)(row0 + r) * nh + h) * A2_D + lane * 4) = packed;
+}
+
 }  // namespace
 
-// Arguments as bf_prefill_attention_umma.  Head size 128 only, pages of 8..64 keys that
+// Arguments as bf_prefill_attention_umma, and: splits > 1 shares the keys of every block of 256
+// queries out over that many CTAs (for few queries after many cached keys); part_o (float
+// [total_rows, nh, splits, 128]) and part_ml (float [total_rows, nh, splits, 2]) take their
+// partial results, which a second kernel merges.  Head size 128 only, pages of 8..64 keys that
 // divide 64; cudaErrorInvalidValue otherwise (nothing launched).
 BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, const void* v_cache,
                                          const int* items, int n_items, int max_rows,
                                          int total_rows, const int* block_tables,
                                          int table_stride, void* out, int nh, int nkv, int d,
                                          int page_size, int num_pages, int window, float scale,
-                                         int* err, cudaStream_t stream) {
+                                         int splits, float* part_o, float* part_ml, int* err,
+                                         cudaStream_t stream) {
   if (n_items <= 0 || max_rows <= 0) return 0;
+  if (splits < 1 || (splits > 1 && (!part_o || !part_ml))) return (int)cudaErrorInvalidValue;
   if (d != A2_D || nkv <= 0 || nh % nkv || page_size < 8 || page_size > A2_BN ||
       A2_BN % page_size || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) ||
       ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
@@ -527,7 +607,7 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
                                     A2_BN / page_size);
   if (e) return e;
   // two Q tiles, the stages of K and V, the row sums, barriers
-  const size_t smem = 1024 + (size_t)2 * 32768 + (size_t)2 * A2_STAGES * 16384 + 1024 + 256;
+  const size_t smem = 1024 + (size_t)2 * 32768 + (size_t)2 * A2_STAGES * 16384 + 2048 + 256;
   auto kern = prefill_attention_umma2_kernel;
   static bool configured_on[BF_MAX_DEVICES];
   bool& configured = configured_on[bf_current_device()];
@@ -537,9 +617,15 @@ BF_EXPORT int bf_prefill_attention_umma2(const void* q, const void* k_cache, con
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
-  dim3 grid((max_rows + 2 * A2_BM - 1) / (2 * A2_BM), nh, n_items);
+  dim3 grid((max_rows + 2 * A2_BM - 1) / (2 * A2_BM), nh, n_items * splits);
   kern<<<grid, A2_THREADS, smem, stream>>>(mq, mk, mv, mkr, mvr, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
-                                           window, scale * 1.4426950408889634f, err);
+                                           window, scale * 1.4426950408889634f, splits, part_o, part_ml, err);
+  if (splits > 1) {
+    int st = bf_launch_status();
+    if (st) return st;
+    prefill_attention_merge_kernel<<<dim3((max_rows + 3) / 4, nh, n_items), 128, 0, stream>>>(
+        part_o, part_ml, items, (__nv_bfloat16*)out, nh, splits);
+  }
   return bf_launch_status();
 }

@@ -305,18 +305,26 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _launches += 1          # two kernels: the splits and their merge
 
 
+# scratch for the shares of split prefill attention, per device (grown as needed, up to a limit)
+_prefill_split_scratch = {}
+_PREFILL_SPLIT_BYTES = 256 << 20
+
+
 def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       items: torch.Tensor, n_items: int, max_rows: int,
                       block_tables: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, d: int,
                       window: Optional[int], scale: float, err: torch.Tensor,
-                      variant: str = "auto") -> None:
+                      variant: str = "auto", max_ctx: int = 0, splits: int = 0) -> None:
     """Causal flash attention over the pages for prompt portions (bfloat16 only).
     ``items`` int32 [n, 4]: (request index, first token row, rows, first position).
     ``variant``: ``umma2`` (tcgen05 tensor cores, one CTA per SM with two query tiles sharing a
     K/V ring; head size 128, page sizes 8..64 that divide 64), ``umma`` (two CTAs of one
     query tile per SM; head sizes 64/128, the same page sizes), ``mma_sync`` (every size in
     DECODE_HEAD_DIMS, any page size), or ``auto``: umma2 where it applies and there are
-    blocks of 256 rows for most SMs, else umma where it applies, else mma_sync."""
+    blocks of 256 rows for most SMs, else umma where it applies, else mma_sync.
+    ``max_ctx``: the longest context among the portions, if the caller knows it: few query
+    rows after many cached keys then have their keys shared out over several CTAs of the umma2
+    kernel, whose partial results a second kernel merges (``splits`` forces a number)."""
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"prefill_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
     if variant not in ("auto", "umma2", "umma", "mma_sync"):
@@ -329,12 +337,48 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     if variant == "umma" and not umma_ok or variant == "umma2" and not umma2_ok:
         raise KernelError(f"prefill_attention: the {variant} variant does not take head_dim {d} "
                           f"with pages of {page_size}")
-    # umma2 gives an SM one block of 256 rows: worth it once there are blocks for most SMs
-    # (one portion, 32 heads: 36.8 against 31.5 us at 1024 rows, but 16.8 against 19.7 at 512)
+    # umma2 gives an SM one block of 256 rows.  One portion, 32 heads, umma against umma2:
+    # 12.8 / 15.0 us at 256 rows from position 0, 20.8 / 20.0 at 512, 44.4 / 29.7 at 1024;
+    # after 8192 cached tokens 258 / 162 at 256 rows (58 with the keys shared out, below).
     blocks2 = -(-max_rows // 256) * nh * n_items
-    use2 = umma2_ok and (variant == "umma2" or (variant == "auto" and blocks2 >= 120))
-    if use2 or (umma_ok and variant != "mma_sync"):
-        name = "prefill_attention_umma2" if use2 else "prefill_attention_umma"
+    use2 = umma2_ok and (variant == "umma2" or (variant == "auto" and (
+        blocks2 >= 120 or max_rows > 256 or max_ctx >= 2048)))
+    # Few blocks and long contexts: share the keys of each block out (at least 16 key tiles a
+    # share, at most 8 shares, no more CTAs than SMs).
+    if splits <= 0:
+        splits = 1
+        if umma2_ok and variant in ("auto", "umma2") and not window and blocks2 * 2 <= num_sms(q.device):
+            splits = max(1, min(8, num_sms(q.device) // blocks2, max_ctx // 1024))
+    if splits > 1 and umma2_ok:
+        T = q.shape[0]
+        need = T * nh * splits
+        if need * d * 4 <= _PREFILL_SPLIT_BYTES:
+            key = q.device.index
+            buf = _prefill_split_scratch.get(key)
+            if buf is None or buf[0].numel() < need * d:
+                buf = _prefill_split_scratch[key] = (
+                    torch.empty(need * d, dtype=torch.float32, device=q.device),
+                    torch.empty(need * 2, dtype=torch.float32, device=q.device))
+            _run("prefill_attention_umma2", lib().bf_prefill_attention_umma2,
+                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
+                 _c_int(max_rows), _c_int(T), _ptr(block_tables),
+                 _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv), _c_int(d),
+                 _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
+                 _c_float(scale), _c_int(splits), _ptr(buf[0]), _ptr(buf[1]), _ptr(err),
+                 _stream())
+            global _launches
+            _launches += 1          # two kernels: the shares and their merge
+            return
+    if use2:
+        _run("prefill_attention_umma2", lib().bf_prefill_attention_umma2,
+             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
+             _c_int(max_rows), _c_int(q.shape[0]), _ptr(block_tables),
+             _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv), _c_int(d),
+             _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0), _c_float(scale),
+             _c_int(1), None, None, _ptr(err), _stream())
+        return
+    if umma_ok and variant != "mma_sync":
+        name = "prefill_attention_umma"
         _run(name, getattr(lib(), "bf_" + name),
              _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(items), _c_int(n_items),
              _c_int(max_rows), _c_int(q.shape[0]), _ptr(block_tables),

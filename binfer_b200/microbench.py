@@ -142,7 +142,8 @@ def prefill_attention(a):
     fn = lambda: ops.prefill_attention(q, kc, vc, items, 1, T, bt, out, nh, nkv, d, None,
                                        d ** -0.5, err,
                                        variant=a.variant if a.variant in ("umma2", "umma", "mma_sync")
-                                       else "auto")
+                                       else "auto", max_ctx=ctx if a.splits < 0 else 0,
+                                       splits=max(a.splits, 0))
     us = timed([fn], a.iters, a.warmup)
     flops = 4.0 * nh * d * (T * start + T * (T + 1) / 2)
     report("prefill_attention", us, flops=flops, tokens=T, start=start, heads=nh, kv_heads=nkv,
@@ -307,6 +308,9 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0, help="feature rows per tile (0: chosen)")
     ap.add_argument("--library", action="store_true", help="time cuBLAS on the same product")
+    ap.add_argument("--splits", type=int, default=-1,
+                    help="prefill attention: shares of the keys per block of 256 queries "
+                         "(-1: chosen from the context, 1: none)")
     ap.add_argument("--pair", action="store_true",
                     help="gemm, swiglu: the kernel on pairs of SMs (many token rows)")
     ap.add_argument("--cluster", type=int, default=0,

@@ -207,7 +207,7 @@ class GQAAttention(Mixer):
         if ctx.n_prefill:
             ops.prefill_attention(q, view.k_cache, view.v_cache, ctx.prefill_items,
                                   ctx.n_prefill, ctx.max_prefill_rows, tables, out, *common,
-                                  ctx.err)
+                                  ctx.err, max_ctx=ctx.max_ctx_len)
 
 
 register_mixer("attention", GQAAttention)

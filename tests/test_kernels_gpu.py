@@ -775,6 +775,38 @@ def test_prefill_attention_over_pages(cuda_device, nh, nkv, d, ps, window, spike
     assert torch.equal(out2[70:112], out[70:112]) and float(out2[:70].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("ps,neighbours", [(16, True), (8, False), (64, False)])
+def test_prefill_attention_keys_shared_out(cuda_device, splits, ps, neighbours):
+    """Few queries after many cached keys: the keys of a block of 256 queries are shared out
+    over several CTAs and merged.  Portions whose blocks have fewer key tiles than there are
+    shares (an empty share), rows that see no key of a share (causal), a portion of two rows,
+    and one from position 0, beside long prefixes; the far key is made to stand out."""
+    from binfer_b200.csrc import ops
+    nh, nkv, d = 4, 2, 128
+    ctxs, qlens = [1500, 70, 2100, 2, 900], [200, 70, 300, 2, 129]
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   qlens, None, True, seed=31,
+                                                   neighbours=neighbours)
+    items, row = [], 0
+    for b, (n, ql) in enumerate(zip(ctxs, qlens)):
+        items.append([b, row, ql, n - ql])
+        row += ql
+    items = torch.tensor(items, dtype=torch.int32, device=cuda_device)
+    err = _err(cuda_device)
+    out = torch.zeros_like(q)
+    ops.prefill_attention(q, kc, vc, items, len(ctxs), max(qlens), bt, out, nh, nkv, d, None,
+                          d ** -0.5, err, variant="umma2", splits=splits)
+    assert int(err.item()) == 0
+    _close(out, ref, BF16)
+    # the number of shares chosen from the longest context gives the same values to rounding
+    auto = torch.zeros_like(q)
+    ops.prefill_attention(q, kc, vc, items, len(ctxs), max(qlens), bt, auto, nh, nkv, d, None,
+                          d ** -0.5, err, max_ctx=max(ctxs))
+    assert int(err.item()) == 0
+    _close(auto, ref, BF16)
+
+
 @pytest.mark.parametrize("ps,window,neighbours", [(64, None, False), (16, 300, False),
                                                   (8, None, False), (16, None, True),
                                                   (8, 300, True), (32, 100, True)])
