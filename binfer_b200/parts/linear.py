@@ -46,8 +46,10 @@ def _use_own(M: int, N: int, K: int) -> bool:
 # Fewest token rows from which the gated feed-forward product goes to the kernel on pairs of
 # SMs (``csrc/gemm_tcgen05_pair.cu``, the activation in its epilogue).  Measured against the
 # library's product followed by the activation kernel, 12288 outputs from 4096 inputs:
-# 54 against 41 us at 128 tokens, 56 / 53 at 256, 82 / 82 at 512, 152 / 156 at 1024,
-# 278 / 302 at 2048.  0: never.
+# 54 against 41 us at 128 tokens, 56 / 53 at 256, 82 / 82 at 512, 152 to 165 / 155 at 1024
+# (a tie within the runs' scatter), 276 / 303 at 2048, 515 / 590 at 4096; 6144 outputs from 2048
+# inputs: 83 / 83 at 2048, 138 / 165 at 4096; 25600 from 5120: 355 / 381 at 1024, 678 / 772 at
+# 2048.  0: never.
 _PAIR_MIN_TOKENS = int(os.environ.get("BINFER_B200_PAIR_MIN_TOKENS", "1024"))
 # The plain products stay with the library under "auto": the pair kernel takes 74 / 50 / 148 us
 # where the library takes 71 / 46 / 136 (2048 tokens; q/k/v, output and down projection).
