@@ -325,6 +325,7 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     ``max_ctx``: the longest context among the portions, if the caller knows it: few query
     rows after many cached keys then have their keys shared out over several CTAs of the umma2
     kernel, whose partial results a second kernel merges (``splits`` forces a number)."""
+    global _launches
     if q.dtype != torch.bfloat16 or d not in DECODE_HEAD_DIMS:
         raise KernelError(f"prefill_attention: bfloat16 and head_dim in {DECODE_HEAD_DIMS} only")
     if variant not in ("auto", "umma2", "umma", "mma_sync"):
@@ -366,7 +367,6 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                  _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
                  _c_float(scale), _c_int(splits), _ptr(buf[0]), _ptr(buf[1]), _ptr(err),
                  _stream())
-            global _launches
             _launches += 1          # two kernels: the shares and their merge
             return
     if use2:
