@@ -248,6 +248,55 @@ def serve_point(peaks, layers=None, page_size=PAGE_SIZE):
     return r
 
 
+def profile_steps(args):
+    """Per-kernel time of one prefill step and of one decode step, eager (event pairs around
+    every launch: short kernels read longer than inside a captured step, so shares, not
+    sums, are what to read)."""
+    import torch
+    from binfer_b200 import Engine, Qwen3Config
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.profiling import Profiler
+    base, shape_name, context, batches = SHAPES[args.shape]
+    raw = dict(base)
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = Qwen3Config.from_dict(raw)
+    B = args.batch or batches[1]
+    ps = args.page_size
+    engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=B * (context // ps) + 64 + 256,
+                    page_size=ps, max_seq_len=context, max_batch_size=B + 1,
+                    max_tokens_per_step=2048, cuda_graphs=False)
+    runner = engine.runner
+    gen = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+
+    def prefill():
+        runner.add_request("pf")
+        runner.step([StepItem("pf", toks, [PREFILL_TOKENS - 1])])
+        runner.free_request("pf")
+
+    rids = fill_cache(engine, runner, B, context - 16, cfg.vocab_size, gen)
+    decode_items = [StepItem(r, [7 + i], [0]) for i, r in enumerate(rids)]
+    n = 3
+    for name, fn in ((f"prefill of {PREFILL_TOKENS} tokens", prefill),
+                     (f"decode step, batch {B}, context {context}", lambda: runner.step(decode_items))):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        prof = Profiler()
+        for _ in range(n):
+            fn()
+        prof.stop()
+        rows = sorted(prof.collect().items(), key=lambda kv: -kv[1][1])
+        total = sum(ms for _, (_, ms) in rows)
+        print(f"\n{shape_name} shape, {cfg.num_hidden_layers} layers: {name} "
+              f"(mean of {n}, {total / n:.2f} ms of kernels)")
+        for kernel, (calls, ms) in rows:
+            print(f"  {kernel:<30}{calls // n:>6} calls{ms / n:>10.3f} ms{100 * ms / total:>7.1f} %")
+    runner.check_errors()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -267,6 +316,10 @@ def main():
     ap.add_argument("--decode-only", action="store_true",
                     help="only the device-timed decode steps (for profiling): no e2e, no points")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for profiling)")
+    ap.add_argument("--profile", action="store_true",
+                    help="instead of the bench line: per-kernel CUDA events of a prefill of 2,048 "
+                         "tokens and of a decode step at --batch (eager launches; the "
+                         "reference's spans: src/profiler/profiler.ts:93-479)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -275,6 +328,8 @@ def main():
         return 2
     args.warmup = max(args.warmup, 3)
     peaks = load_peaks()
+    if args.profile:
+        return profile_steps(args)
     if args.workload == "serve":
         r = serve_point(peaks, args.layers, args.page_size)
         print(json.dumps({"metric": "continuous batching, 64 requests x [128, 2048] prompt "
