@@ -493,7 +493,7 @@ int launch(const void* x, const void* w, OutT* out, PairParams p, long long ldx,
 }  // namespace
 
 // Accumulator columns per tile (a multiple of `step`, at most 256) for `tokens` x `columns`
-// on num_sms / 2 pairs: the width that wastes least of the last round of tiles, wider tiles
+// on num_sms / 2 pairs: the width that wastes least of the last wave of tiles, wider tiles
 // preferred when there is little to choose (they reuse the token rows more).
 BF_EXPORT int bf_gemm_pair_choose_bn(int tokens, int columns, int step, int num_sms) {
   const int tiles_t = (tokens + PM - 1) / PM;
