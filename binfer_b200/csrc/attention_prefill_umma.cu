@@ -100,10 +100,11 @@ prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap map_q,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int* it = items + 4 * blockIdx.z;
+  const int* it = items + 4 * blockIdx.y;
   const int seq = it[0], row0 = it[1], qlen = it[2], pos0 = it[3];
   // the last query tiles see the most keys: they are launched first
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
+  // (z, the slowest index of the hand-out, counts the query tiles down: the longest first)
+  const int qt = (int)gridDim.z - 1 - (int)blockIdx.z, h = blockIdx.x;
   if (qt * AU_BM >= qlen) return;
   const int g = h / (nh / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -443,7 +444,8 @@ int launch_umma(const void* q, const void* k_cache, const void* v_cache, const i
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
-  dim3 grid((max_rows + AU_BM - 1) / AU_BM, nh, n_items);
+  dim3 grid(nh, n_items, (max_rows + AU_BM - 1) / AU_BM);
+  if (grid.y > 65535u || grid.z > 65535u) return (int)cudaErrorInvalidValue;
   kern<<<grid, AU_THREADS, smem, stream>>>(mq, mk, mv, mkr, mvr, items, block_tables, table_stride,
                                            (__nv_bfloat16*)out, nh, nkv, page_size, num_pages,
                                            window, scale * 1.4426950408889634f, err);
