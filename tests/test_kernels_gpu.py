@@ -807,6 +807,42 @@ def test_prefill_attention_keys_shared_out(cuda_device, splits, ps, neighbours):
     _close(auto, ref, BF16)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_prefill_attention_random_shapes(cuda_device, seed):
+    """Shapes drawn at random (heads, groups, page size, window, how many portions, where they
+    start and how long they are, pages side by side or scattered): the kernel that the policy
+    picks, with the keys shared out or not as it decides, against the plain result."""
+    import random
+    from binfer_b200.csrc import ops
+    rnd = random.Random(seed)
+    nkv = rnd.choice([1, 2, 4])
+    nh = nkv * rnd.choice([1, 2, 4, 7])
+    d, ps = 128, rnd.choice([8, 16, 32, 64])
+    window = rnd.choice([None, None, rnd.randint(40, 900)])
+    n = rnd.randint(1, 4)
+    qlens = [rnd.choice([2, rnd.randint(3, 130), rnd.randint(131, 700)]) for _ in range(n)]
+    ctxs = [ql + rnd.choice([0, rnd.randint(1, 300), rnd.randint(1500, 3000)]) for ql in qlens]
+    q, kc, vc, sot, pos, bt, ref = _attention_case(cuda_device, BF16, nh, nkv, d, ps, ctxs,
+                                                   qlens, window, True, seed=100 + seed,
+                                                   neighbours=rnd.random() < 0.5)
+    items, row = [], 0
+    for b, (c, ql) in enumerate(zip(ctxs, qlens)):
+        items.append([b, row, ql, c - ql])
+        row += ql
+    items = torch.tensor(items, dtype=torch.int32, device=cuda_device)
+    err = _err(cuda_device)
+    out = torch.zeros_like(q)
+    ops.prefill_attention(q, kc, vc, items, n, max(qlens), bt, out, nh, nkv, d, window,
+                          d ** -0.5, err, max_ctx=max(ctxs))
+    assert int(err.item()) == 0
+    _close(out, ref, BF16)
+    two = torch.zeros_like(q)
+    ops.prefill_attention(q, kc, vc, items, n, max(qlens), bt, two, nh, nkv, d, window,
+                          d ** -0.5, err, variant="umma2", splits=1)
+    assert int(err.item()) == 0
+    _close(two, ref, BF16)
+
+
 @pytest.mark.parametrize("ps,window,neighbours", [(64, None, False), (16, 300, False),
                                                   (8, None, False), (16, None, True),
                                                   (8, 300, True), (32, 100, True)])
